@@ -1,0 +1,274 @@
+"""ctypes binding of ``libdfl_b200.so`` (the C ABI in ``include/dfl_b200.h``).
+
+PyTorch is used here only as the owner of device memory and of the current
+CUDA stream: every wrapper takes tensors, checks layout, and passes raw
+device pointers plus sizes to the C functions.  There is no Python or CPU
+implementation behind these calls; if the library is missing the import
+fails loudly.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+from pathlib import Path
+
+import torch
+
+LIB_PATH = Path(__file__).resolve().parent / "libdfl_b200.so"
+
+DFL_F16, DFL_BF16, DFL_F32 = 0, 1, 2
+ALGO_AUTO, ALGO_SIMT = 0, 1
+
+DFL_ERR_BAD_ARG = -1
+DFL_ERR_UNSUPPORTED = -2
+DFL_ERR_ALIGNMENT = -3
+DFL_ERR_LAUNCH = -4
+DFL_ERR_DRIVER = -5
+DFL_ERR_DEVICE_TIMEOUT = -6
+DFL_ERR_TOO_LARGE = -7
+
+_DTYPES = {torch.float16: DFL_F16, torch.bfloat16: DFL_BF16, torch.float32: DFL_F32}
+
+EXPORTED_SYMBOLS = (
+    "dfl_version",
+    "dfl_status_string",
+    "dfl_last_error",
+    "dfl_build_position_lut",
+    "dfl_qkv_proj",
+    "dfl_gather_slots",
+    "dfl_pos_scores",
+    "dfl_attention_fwd",
+)
+
+
+class DflLinearParams(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("w", c_void_p), ("bias", c_void_p), ("out", c_void_p * 3),
+        ("M", c_int32), ("K", c_int32), ("n_out", c_int32), ("heads", c_int32), ("head_dim", c_int32),
+        ("rows_per_seq", c_int32), ("dtype", c_int32), ("algo", c_int32),
+    ]
+
+
+class DflPosScoreParams(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k", c_void_p), ("pos_key", c_void_p), ("pos_query", c_void_p),
+        ("c2p", c_void_p), ("p2c", c_void_p),
+        ("batch", c_int32), ("heads", c_int32), ("seq_len", c_int32), ("head_dim", c_int32),
+        ("n_active", c_int32), ("ld_slots", c_int32), ("dtype", c_int32), ("algo", c_int32),
+    ]
+
+
+class DflAttnParams(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("c2p", c_void_p), ("p2c", c_void_p),
+        ("lut", c_void_p), ("mask", c_void_p), ("out", c_void_p), ("status", c_void_p),
+        ("batch", c_int32), ("heads", c_int32), ("seq_len", c_int32), ("head_dim", c_int32),
+        ("ld_slots", c_int32), ("mask_elem_size", c_int32), ("scale", c_float),
+        ("dtype", c_int32), ("algo", c_int32),
+    ]
+
+
+class DflError(RuntimeError):
+    """A C entry point returned a negative status."""
+
+    def __init__(self, status: int, where: str, detail: str):
+        super().__init__(f"{where}: {detail} (status {status})")
+        self.status = status
+
+
+_lib = None
+
+# Optional launch observer: ``callback(name, n_kernels) -> context manager or None``.
+# Benchmarks install one to count launches and to bracket a kernel with CUDA
+# events on the launching stream; it is never set in normal operation.
+_launch_observer = None
+
+
+def set_launch_observer(callback) -> None:
+    global _launch_observer
+    _launch_observer = callback
+
+
+class _NullContext:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+def _observe(name: str, n_kernels: int):
+    if _launch_observer is None:
+        return _NullContext()
+    return _launch_observer(name, n_kernels) or _NullContext()
+
+
+def load_library() -> ctypes.CDLL:
+    """Load the shared library once; raise if it has not been built."""
+
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m disentangled_flash_b200.build` "
+            "(needs nvcc; there is no CPU or PyTorch fallback for these kernels)"
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    lib.dfl_version.restype = c_int
+    lib.dfl_status_string.restype = c_char_p
+    lib.dfl_status_string.argtypes = [c_int]
+    lib.dfl_last_error.restype = c_char_p
+    lib.dfl_build_position_lut.restype = c_int
+    lib.dfl_build_position_lut.argtypes = [c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+    lib.dfl_qkv_proj.restype = c_int
+    lib.dfl_qkv_proj.argtypes = [POINTER(DflLinearParams), c_void_p]
+    lib.dfl_gather_slots.restype = c_int
+    lib.dfl_gather_slots.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    lib.dfl_pos_scores.restype = c_int
+    lib.dfl_pos_scores.argtypes = [POINTER(DflPosScoreParams), c_void_p]
+    lib.dfl_attention_fwd.restype = c_int
+    lib.dfl_attention_fwd.argtypes = [POINTER(DflAttnParams), c_void_p]
+    _lib = lib
+    return lib
+
+
+def _check(status: int, where: str) -> None:
+    if status == 0:
+        return
+    lib = load_library()
+    detail = (lib.dfl_last_error() or b"").decode() or lib.dfl_status_string(status).decode()
+    if status in (DFL_ERR_BAD_ARG, DFL_ERR_ALIGNMENT, DFL_ERR_TOO_LARGE):
+        raise ValueError(f"{where}: {detail} (status {status})")
+    raise DflError(status, where, detail)
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise TypeError("the B200 path supports FP16, BF16, and FP32") from None
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _require_cuda_contiguous(name: str, t: torch.Tensor) -> None:
+    if t.device.type != "cuda":
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def build_position_lut(seq_len: int, position_buckets: int, max_relative_positions: int, span: int,
+                       uses_position_bias: bool, device: torch.device):
+    """Run the index-builder kernel; returns ``(active_slots int64[A], delta_to_local int32[2L-1])``."""
+
+    lib = load_library()
+    if seq_len < 1:
+        raise ValueError("sequence_length must be positive")
+    n = 2 * seq_len - 1
+    cap = max(1, min(n, 2 * max(span, 1)))
+    with torch.cuda.device(device):
+        lut = torch.empty(n, dtype=torch.int32, device=device)
+        active = torch.empty(cap, dtype=torch.int64, device=device)
+        count = torch.zeros(1, dtype=torch.int32, device=device)
+        _check(lib.dfl_build_position_lut(seq_len, position_buckets, max_relative_positions, span,
+                                          int(uses_position_bias), lut.data_ptr(), active.data_ptr(),
+                                          count.data_ptr(), _stream(device)), "dfl_build_position_lut")
+        n_active = int(count.item())  # prepare-time only: one 4-byte read-back per bucket length
+    return active[:n_active].clone(), lut
+
+
+def linear_heads(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, *, n_out: int, heads: int,
+                 head_dim: int, rows_per_seq: int, algo: int = ALGO_AUTO) -> tuple[torch.Tensor, ...]:
+    """``x[M,K] @ weight[N,K]^T + bias`` written as ``n_out`` tensors ``[M/rows, heads, rows, head_dim]``."""
+
+    lib = load_library()
+    _require_cuda_contiguous("x", x)
+    _require_cuda_contiguous("weight", weight)
+    x2 = x.reshape(-1, x.shape[-1])
+    m, k = x2.shape
+    if weight.shape != (n_out * heads * head_dim, k):
+        raise ValueError(f"weight shape {tuple(weight.shape)} does not match [{n_out * heads * head_dim}, {k}]")
+    outs = tuple(torch.empty(m // rows_per_seq, heads, rows_per_seq, head_dim, dtype=x.dtype, device=x.device)
+                 for _ in range(n_out))
+    p = DflLinearParams()
+    p.x, p.w, p.bias = x2.data_ptr(), weight.data_ptr(), _ptr(bias)
+    for i, o in enumerate(outs):
+        p.out[i] = o.data_ptr()
+    p.M, p.K, p.n_out, p.heads, p.head_dim, p.rows_per_seq = m, k, n_out, heads, head_dim, rows_per_seq
+    p.dtype, p.algo = dtype_code(x.dtype), algo
+    with torch.cuda.device(x.device), _observe("dfl_qkv_proj", 1):
+        _check(lib.dfl_qkv_proj(ctypes.byref(p), _stream(x.device)), "dfl_qkv_proj")
+    return outs
+
+
+def gather_slots(src: torch.Tensor, active: torch.Tensor) -> torch.Tensor:
+    """``src[H, S, d] -> [H, A, d]`` by the active-slot list."""
+
+    lib = load_library()
+    _require_cuda_contiguous("src", src)
+    heads, n_src, d = src.shape
+    n_active = active.numel()
+    dst = torch.empty(heads, n_active, d, dtype=src.dtype, device=src.device)
+    with torch.cuda.device(src.device):
+        _check(lib.dfl_gather_slots(src.data_ptr(), active.data_ptr(), dst.data_ptr(), heads, n_src, n_active, d,
+                                    dtype_code(src.dtype), _stream(src.device)), "dfl_gather_slots")
+    return dst
+
+
+def padded_slots(n_active: int) -> int:
+    """Leading dimension of the position-score tensors: rows stay 16-byte aligned."""
+
+    return max(8, (n_active + 7) // 8 * 8)
+
+
+def pos_scores(q: torch.Tensor | None, k: torch.Tensor | None, pos_key: torch.Tensor | None,
+               pos_query: torch.Tensor | None, *, algo: int = ALGO_AUTO):
+    """C2P / P2C score GEMMs over the active slots; returns ``(c2p, p2c, ld_slots)``."""
+
+    lib = load_library()
+    ref = q if q is not None else k
+    bsz, heads, length, d = ref.shape
+    n_active = (pos_key if pos_key is not None else pos_query).shape[1]
+    ld = padded_slots(n_active)
+    c2p = torch.empty(bsz, heads, length, ld, dtype=ref.dtype, device=ref.device) if pos_key is not None else None
+    p2c = torch.empty(bsz, heads, length, ld, dtype=ref.dtype, device=ref.device) if pos_query is not None else None
+    p = DflPosScoreParams()
+    p.q, p.k = _ptr(q) if pos_key is not None else None, _ptr(k) if pos_query is not None else None
+    p.pos_key, p.pos_query, p.c2p, p.p2c = _ptr(pos_key), _ptr(pos_query), _ptr(c2p), _ptr(p2c)
+    p.batch, p.heads, p.seq_len, p.head_dim = bsz, heads, length, d
+    p.n_active, p.ld_slots, p.dtype, p.algo = n_active, ld, dtype_code(ref.dtype), algo
+    with torch.cuda.device(ref.device), _observe("dfl_pos_scores", int(c2p is not None) + int(p2c is not None)):
+        _check(lib.dfl_pos_scores(ctypes.byref(p), _stream(ref.device)), "dfl_pos_scores")
+    return c2p, p2c, ld
+
+
+def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, c2p: torch.Tensor | None,
+                  p2c: torch.Tensor | None, lut: torch.Tensor | None, mask: torch.Tensor, scale: float, *,
+                  ld_slots: int = 0, algo: int = ALGO_AUTO, status: torch.Tensor | None = None) -> torch.Tensor:
+    """Fused attention; ``q,k,v`` are ``[B,H,L,d]``, result is ``[B,L,H*d]``."""
+
+    lib = load_library()
+    for name, t in (("q", q), ("k", k), ("v", v), ("mask", mask)):
+        _require_cuda_contiguous(name, t)
+    bsz, heads, length, d = q.shape
+    if mask.element_size() not in (1, 4, 8) or mask.dtype.is_floating_point:
+        raise TypeError("mask must be a bool or integer tensor")
+    out = torch.empty(bsz, length, heads * d, dtype=q.dtype, device=q.device)
+    p = DflAttnParams()
+    p.q, p.k, p.v, p.c2p, p.p2c = q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(c2p), _ptr(p2c)
+    p.lut, p.mask, p.out, p.status = _ptr(lut), mask.data_ptr(), out.data_ptr(), _ptr(status)
+    p.batch, p.heads, p.seq_len, p.head_dim = bsz, heads, length, d
+    p.ld_slots, p.mask_elem_size, p.scale = ld_slots, mask.element_size(), scale
+    p.dtype, p.algo = dtype_code(q.dtype), algo
+    with torch.cuda.device(q.device), _observe("dfl_attention_fwd", 1):
+        _check(lib.dfl_attention_fwd(ctypes.byref(p), _stream(q.device)), "dfl_attention_fwd")
+    return out

@@ -1,0 +1,145 @@
+// extern "C" entry points: argument validation and dispatch only.
+#include "dfl_common.cuh"
+
+using namespace dfl;
+
+namespace {
+
+bool valid_dtype(int d) { return d == DFL_F16 || d == DFL_BF16 || d == DFL_F32; }
+bool valid_head_dim(int d) { return d == 32 || d == 64 || d == 128; }
+bool use_tensor_cores(int dtype, int algo) { return algo == DFL_ALGO_AUTO && dtype != DFL_F32; }
+
+}  // namespace
+
+extern "C" {
+
+int dfl_version(void) { return 100; }
+
+const char* dfl_status_string(int status) {
+  switch (status) {
+    case DFL_OK: return "ok";
+    case DFL_ERR_BAD_ARG: return "bad argument";
+    case DFL_ERR_UNSUPPORTED: return "unsupported configuration";
+    case DFL_ERR_ALIGNMENT: return "pointer or leading dimension not 16-byte aligned";
+    case DFL_ERR_LAUNCH: return "CUDA launch failed";
+    case DFL_ERR_DRIVER: return "CUDA driver call failed";
+    case DFL_ERR_DEVICE_TIMEOUT: return "device-side bounded wait expired";
+    case DFL_ERR_TOO_LARGE: return "size beyond supported maximum";
+  }
+  return "unknown status";
+}
+
+const char* dfl_last_error(void) { return last_error_buffer(); }
+
+int dfl_build_position_lut(int seq_len, int position_buckets, int max_relative_positions, int span,
+                           int uses_position_bias, int32_t* lut_dev, int64_t* active_dev,
+                           int32_t* n_active_dev, void* stream) {
+  if (seq_len < 1) return fail(DFL_ERR_BAD_ARG, "sequence_length must be positive");
+  if (!lut_dev || !n_active_dev) return fail(DFL_ERR_BAD_ARG, "null output pointer");
+  if (uses_position_bias) {
+    if (!active_dev) return fail(DFL_ERR_BAD_ARG, "null active_slots pointer");
+    if (span < 1) return fail(DFL_ERR_BAD_ARG, "span must be positive");
+    if (position_buckets == 1) return fail(DFL_ERR_BAD_ARG, "position_buckets == 1 has no valid bucket map");
+    if (position_buckets > 1 && max_relative_positions - 1 <= position_buckets / 2)
+      return fail(DFL_ERR_BAD_ARG, "max_relative_positions-1 must exceed position_buckets/2");
+  }
+  if (seq_len > (1 << 20)) return fail(DFL_ERR_TOO_LARGE, "sequence_length > 2^20");
+  return launch_position_lut(seq_len, position_buckets, max_relative_positions, span,
+                             uses_position_bias, lut_dev, active_dev, n_active_dev,
+                             (cudaStream_t)stream);
+}
+
+int dfl_gather_slots(const void* src, const int64_t* active_dev, void* dst, int heads,
+                     int n_slots_src, int n_active, int head_dim, int dtype, void* stream) {
+  if (!valid_dtype(dtype)) return fail(DFL_ERR_BAD_ARG, "unknown dtype %d", dtype);
+  if (heads < 1 || n_slots_src < 1 || n_active < 0 || head_dim < 1)
+    return fail(DFL_ERR_BAD_ARG, "non-positive size");
+  if (n_active == 0) return DFL_OK;
+  if (!src || !active_dev || !dst) return fail(DFL_ERR_BAD_ARG, "null pointer");
+  return launch_gather_slots(src, active_dev, dst, heads, n_slots_src, n_active, head_dim, dtype,
+                             (cudaStream_t)stream);
+}
+
+int dfl_qkv_proj(const DflLinearParams* p, void* stream) {
+  if (!p) return fail(DFL_ERR_BAD_ARG, "null params");
+  if (!valid_dtype(p->dtype)) return fail(DFL_ERR_BAD_ARG, "unknown dtype %d", p->dtype);
+  if (p->n_out < 1 || p->n_out > 3) return fail(DFL_ERR_BAD_ARG, "n_out must be 1..3");
+  if (p->M < 1 || p->K < 1 || p->heads < 1 || p->rows_per_seq < 1)
+    return fail(DFL_ERR_BAD_ARG, "non-positive size");
+  if (!valid_head_dim(p->head_dim))
+    return fail(DFL_ERR_UNSUPPORTED, "head_dim %d not in {32,64,128}", p->head_dim);
+  if (p->M % p->rows_per_seq) return fail(DFL_ERR_BAD_ARG, "M not a multiple of rows_per_seq");
+  if (!p->x || !p->w) return fail(DFL_ERR_BAD_ARG, "null input pointer");
+  if (!aligned16(p->x) || !aligned16(p->w)) return fail(DFL_ERR_ALIGNMENT, "x/w not 16-byte aligned");
+  for (int o = 0; o < p->n_out; ++o) {
+    if (!p->out[o]) return fail(DFL_ERR_BAD_ARG, "null output pointer %d", o);
+    if (!aligned16(p->out[o])) return fail(DFL_ERR_ALIGNMENT, "output %d not 16-byte aligned", o);
+  }
+  GemmDesc g{};
+  g.x = p->x; g.w = p->w; g.bias = p->bias;
+  for (int o = 0; o < 3; ++o) g.out[o] = o < p->n_out ? p->out[o] : nullptr;
+  g.M = p->M; g.N = p->n_out * p->heads * p->head_dim; g.K = p->K;
+  g.batch = 1; g.stride_x = 0; g.stride_w = 0; g.w_mod = 1; g.stride_c = 0; g.ldc = g.N;
+  g.head_split = 1; g.heads = p->heads; g.head_dim = p->head_dim; g.rows_per_seq = p->rows_per_seq;
+  g.dtype = p->dtype;
+  if (use_tensor_cores(p->dtype, p->algo)) return launch_gemm_tc(g, (cudaStream_t)stream);
+  return launch_gemm_simt(g, (cudaStream_t)stream);
+}
+
+int dfl_pos_scores(const DflPosScoreParams* p, void* stream) {
+  if (!p) return fail(DFL_ERR_BAD_ARG, "null params");
+  if (!valid_dtype(p->dtype)) return fail(DFL_ERR_BAD_ARG, "unknown dtype %d", p->dtype);
+  if (p->batch < 1 || p->heads < 1 || p->seq_len < 1 || p->n_active < 1)
+    return fail(DFL_ERR_BAD_ARG, "non-positive size");
+  if (!valid_head_dim(p->head_dim))
+    return fail(DFL_ERR_UNSUPPORTED, "head_dim %d not in {32,64,128}", p->head_dim);
+  if (p->ld_slots < p->n_active || p->ld_slots % 8)
+    return fail(DFL_ERR_ALIGNMENT, "ld_slots must be >= n_active and a multiple of 8");
+  if ((long long)p->batch * p->heads > 65535) return fail(DFL_ERR_TOO_LARGE, "batch*heads > 65535");
+  int rc = DFL_OK;
+  for (int term = 0; term < 2 && rc == DFL_OK; ++term) {
+    const void* x = term == 0 ? p->q : p->k;
+    const void* w = term == 0 ? p->pos_key : p->pos_query;
+    void* out = term == 0 ? p->c2p : p->p2c;
+    if (!out) continue;
+    if (!x || !w) return fail(DFL_ERR_BAD_ARG, "null input for requested position-score term %d", term);
+    if (!aligned16(x) || !aligned16(w) || !aligned16(out))
+      return fail(DFL_ERR_ALIGNMENT, "position-score tensor not 16-byte aligned");
+    GemmDesc g{};
+    g.x = x; g.w = w; g.bias = nullptr; g.out[0] = out;
+    g.M = p->seq_len; g.N = p->n_active; g.K = p->head_dim;
+    g.batch = p->batch * p->heads;
+    g.stride_x = (long long)p->seq_len * p->head_dim;
+    g.stride_w = (long long)p->n_active * p->head_dim;
+    g.w_mod = p->heads;
+    g.stride_c = (long long)p->seq_len * p->ld_slots;
+    g.ldc = p->ld_slots;
+    g.head_split = 0; g.heads = p->heads; g.head_dim = p->head_dim; g.rows_per_seq = p->seq_len;
+    g.dtype = p->dtype;
+    rc = use_tensor_cores(p->dtype, p->algo) ? launch_gemm_tc(g, (cudaStream_t)stream)
+                                             : launch_gemm_simt(g, (cudaStream_t)stream);
+  }
+  return rc;
+}
+
+int dfl_attention_fwd(const DflAttnParams* p, void* stream) {
+  if (!p) return fail(DFL_ERR_BAD_ARG, "null params");
+  if (!valid_dtype(p->dtype)) return fail(DFL_ERR_BAD_ARG, "unknown dtype %d", p->dtype);
+  if (p->batch < 1 || p->heads < 1 || p->seq_len < 1) return fail(DFL_ERR_BAD_ARG, "non-positive size");
+  if (!valid_head_dim(p->head_dim))
+    return fail(DFL_ERR_UNSUPPORTED, "head_dim %d not in {32,64,128}", p->head_dim);
+  if (!p->q || !p->k || !p->v || !p->out || !p->mask) return fail(DFL_ERR_BAD_ARG, "null pointer");
+  if (p->mask_elem_size != 1 && p->mask_elem_size != 4 && p->mask_elem_size != 8)
+    return fail(DFL_ERR_BAD_ARG, "mask_elem_size must be 1, 4 or 8");
+  if ((p->c2p || p->p2c) && !p->lut) return fail(DFL_ERR_BAD_ARG, "position scores given without a LUT");
+  if ((p->c2p || p->p2c) && (p->ld_slots < 1 || p->ld_slots % 8))
+    return fail(DFL_ERR_ALIGNMENT, "ld_slots must be a positive multiple of 8");
+  if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out) ||
+      (p->c2p && !aligned16(p->c2p)) || (p->p2c && !aligned16(p->p2c)))
+    return fail(DFL_ERR_ALIGNMENT, "attention tensor not 16-byte aligned");
+  if (!(p->scale > 0.0f)) return fail(DFL_ERR_BAD_ARG, "scale must be positive");
+  if (use_tensor_cores(p->dtype, p->algo)) return launch_attention_tc(*p, (cudaStream_t)stream);
+  return launch_attention_simt(*p, (cudaStream_t)stream);
+}
+
+}  // extern "C"

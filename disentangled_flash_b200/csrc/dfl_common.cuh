@@ -1,0 +1,102 @@
+// Shared host/device helpers for the B200 disentangled-attention library.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/dfl_b200.h"
+
+namespace dfl {
+
+// ---------------------------------------------------------------- errors ---
+// Last error detail, per host thread.  Written only on failure paths.
+inline char* last_error_buffer() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+
+inline int fail(int status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(last_error_buffer(), 512, fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+  return DFL_OK;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline size_t dtype_size(int dtype) { return dtype == DFL_F32 ? 4 : 2; }
+
+// ------------------------------------------------------------ conversions ---
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+  static __device__ __forceinline__ float to_f(float v) { return v; }
+  static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+template <> struct Elem<__half> {
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+};
+template <> struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+
+// Round an fp32 value through T (identity for float).
+template <typename T>
+__device__ __forceinline__ float round_through(float v) {
+  return Elem<T>::to_f(Elem<T>::from_f(v));
+}
+
+// Non-zero test of one mask element of 1, 4 or 8 bytes.
+__device__ __forceinline__ bool mask_keep(const void* mask, int elem_size, long long idx) {
+  if (elem_size == 1) return reinterpret_cast<const uint8_t*>(mask)[idx] != 0;
+  if (elem_size == 4) return reinterpret_cast<const uint32_t*>(mask)[idx] != 0;
+  return reinterpret_cast<const unsigned long long*>(mask)[idx] != 0ull;
+}
+
+// ------------------------------------------------- kernel launch wrappers ---
+// One function per kernel family; defined in the matching .cu file.
+int launch_position_lut(int L, int buckets, int max_pos, int span, int uses_bias, int32_t* lut,
+                        int64_t* active, int32_t* n_active, cudaStream_t stream);
+int launch_gather_slots(const void* src, const int64_t* active, void* dst, int heads, int n_src,
+                        int n_active, int d, int dtype, cudaStream_t stream);
+
+// Generic batched "NT" GEMM description used by both GEMM families:
+//   C_z[m, n] = sum_k X_z[m, k] * W_{z % w_mod}[n, k] (+ bias[n])
+// with either a head-split epilogue (QKV / position projection) or a plain
+// row-major epilogue with leading dimension ldc (position scores).
+struct GemmDesc {
+  const void* x;
+  const void* w;
+  const void* bias;
+  void* out[3];
+  int M, N, K;
+  int batch;            // grid.z
+  long long stride_x;   // elements between X_z
+  long long stride_w;   // elements between W_z'
+  int w_mod;            // W index = z % w_mod
+  long long stride_c;   // elements between C_z (row-major epilogue)
+  int ldc;              // row-major epilogue leading dimension; columns [N, ldc) zero-filled
+  int head_split;       // 1: head-split epilogue, 0: row-major
+  int heads, head_dim, rows_per_seq;
+  int dtype;
+};
+int launch_gemm_simt(const GemmDesc& g, cudaStream_t stream);
+int launch_gemm_tc(const GemmDesc& g, cudaStream_t stream);
+
+int launch_attention_simt(const DflAttnParams& p, cudaStream_t stream);
+int launch_attention_tc(const DflAttnParams& p, cudaStream_t stream);
+
+}  // namespace dfl

@@ -1,0 +1,160 @@
+/*
+ * dfl_b200.h -- C ABI of the B200 (sm_100a) disentangled-attention library.
+ *
+ * Every entry point replaces one step of the reference's Triton-backend hot
+ * path (paths below are inside the reference project,
+ * src/disentangled_flash/...).  The library owns no user-visible memory:
+ * every pointer is a borrowed CUDA device pointer unless stated otherwise,
+ * every launch goes to the stream that is passed in, and nothing
+ * synchronises with the host.  All functions return 0 on success or a
+ * negative DFL_ERR_* code; none throws, aborts or prints.
+ *
+ * Alignment: every tensor base pointer must be 16-byte aligned (TMA and
+ * 128-bit vector access); violations return DFL_ERR_ALIGNMENT.
+ */
+#ifndef DFL_B200_H_
+#define DFL_B200_H_
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define DFL_API __attribute__((visibility("default")))
+#else
+#define DFL_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------ */
+#define DFL_OK                   0
+#define DFL_ERR_BAD_ARG         -1  /* null pointer, non-positive size, unknown enum      */
+#define DFL_ERR_UNSUPPORTED     -2  /* head_dim not in {32,64,128}, dtype/algo mismatch   */
+#define DFL_ERR_ALIGNMENT       -3  /* pointer or leading dimension not 16-byte aligned   */
+#define DFL_ERR_LAUNCH          -4  /* CUDA runtime reported an error at launch           */
+#define DFL_ERR_DRIVER          -5  /* tensor-map encoding / driver entry point failed    */
+#define DFL_ERR_DEVICE_TIMEOUT  -6  /* a bounded device-side wait expired (status word)   */
+#define DFL_ERR_TOO_LARGE       -7  /* size beyond a documented fixed maximum             */
+
+/* element type of activations and weights */
+#define DFL_F16   0
+#define DFL_BF16  1
+#define DFL_F32   2
+
+/* kernel family selection: AUTO = tcgen05 kernels for F16/BF16, IEEE-fp32
+ * CUDA-core kernels for F32.  SIMT forces the CUDA-core kernels for any
+ * dtype; it exists so that tests can cross-check the tensor-core kernels at
+ * sizes where a CPU oracle is too slow. */
+#define DFL_ALGO_AUTO  0
+#define DFL_ALGO_SIMT  1
+
+DFL_API int         dfl_version(void);
+DFL_API const char* dfl_status_string(int status);
+/* Human-readable detail of the last non-zero status returned on this host thread. */
+DFL_API const char* dfl_last_error(void);
+
+/*
+ * Log-bucket relative-position index builder (bit-exact).
+ * Replaces SharedPositionPlanCache.compact (position.py:89-128) and
+ * make_log_bucket_position (_reference.py:115-136), which the reference
+ * evaluates on the CPU and copies to the device.
+ *
+ *   lut_dev      int32 [2*seq_len-1]  delta index (i-j+L-1) -> local slot
+ *   active_dev   int64 [min(2*seq_len-1, 2*span)] capacity; first *n_active valid
+ *   n_active_dev int32 [1]
+ * position_buckets <= 0 selects the un-bucketed branch; uses_position_bias == 0
+ * writes an all-zero LUT and n_active = 0 (position.py:118-120).
+ */
+DFL_API int dfl_build_position_lut(int seq_len, int position_buckets, int max_relative_positions,
+                           int span, int uses_position_bias,
+                           int32_t* lut_dev, int64_t* active_dev, int32_t* n_active_dev,
+                           void* stream);
+
+/*
+ * Fused projection with head-split epilogue:
+ *     Y = X[M,K] * W[N,K]^T + bias[N],   N = n_out * heads * head_dim
+ * and column block `o` of Y is written to out[o] in [M/rows_per_seq, heads,
+ * rows_per_seq, head_dim] layout.  With n_out = 3 this is the fused QKV
+ * projection plus the three head transposes (replaces _project_qkv,
+ * _torch.py:284-297, and _reshape_heads x3, _torch.py:299-314).  With
+ * n_out = 1, M = rows_per_seq = 2*span it is the relative-embedding
+ * projection posK/posQ = transpose_for_scores(proj(rel)) (_torch.py:143-158).
+ */
+typedef struct DflLinearParams {
+  const void* x;        /* [M, K] row-major                                    */
+  const void* w;        /* [N, K] row-major (nn.Linear weight layout)          */
+  const void* bias;     /* [N] or NULL                                         */
+  void*       out[3];   /* n_out tensors, each [M/rows_per_seq, heads, rows_per_seq, head_dim] */
+  int32_t M, K;
+  int32_t n_out;        /* 1..3                                                */
+  int32_t heads, head_dim;
+  int32_t rows_per_seq; /* L; M must be a multiple of it                       */
+  int32_t dtype;        /* DFL_F16 / DFL_BF16 / DFL_F32                        */
+  int32_t algo;         /* DFL_ALGO_*                                          */
+} DflLinearParams;
+DFL_API int dfl_qkv_proj(const DflLinearParams* p, void* stream);
+
+/*
+ * Prune projected position tables to the active slots:
+ *   dst[h, a, :] = src[h, active[a], :]      (replaces _project_active_positions,
+ *   _torch.py:171-186).  src is [heads, n_slots_src, head_dim], dst is
+ *   [heads, n_active, head_dim].
+ */
+DFL_API int dfl_gather_slots(const void* src, const int64_t* active_dev, void* dst,
+                     int heads, int n_slots_src, int n_active, int head_dim, int dtype,
+                     void* stream);
+
+/*
+ * Content-to-position / position-to-content score GEMMs over the active slots
+ * (replaces the two torch.matmul calls at kernel.py:574-585):
+ *     c2p[b,h,i,a] = sum_d q[b,h,i,d] * pos_key[h,a,d]
+ *     p2c[b,h,j,a] = sum_d k[b,h,j,d] * pos_query[h,a,d]
+ * Outputs are [batch, heads, seq_len, ld_slots] with ld_slots >= n_active and
+ * ld_slots a multiple of 8 (row starts stay 16-byte aligned); columns
+ * [n_active, ld_slots) are written as zero.  Either pair may be NULL.
+ */
+typedef struct DflPosScoreParams {
+  const void* q;          /* [B,H,L,d] or NULL */
+  const void* k;          /* [B,H,L,d] or NULL */
+  const void* pos_key;    /* [H,A,d]  (needed with q) */
+  const void* pos_query;  /* [H,A,d]  (needed with k) */
+  void*       c2p;        /* [B,H,L,ld_slots] or NULL */
+  void*       p2c;        /* [B,H,L,ld_slots] or NULL */
+  int32_t batch, heads, seq_len, head_dim;
+  int32_t n_active, ld_slots;
+  int32_t dtype, algo;
+} DflPosScoreParams;
+DFL_API int dfl_pos_scores(const DflPosScoreParams* p, void* stream);
+
+/*
+ * Fused disentangled attention forward (replaces the Triton kernel
+ * _deberta_attention_forward_kernel and its launcher, kernel.py:137-429):
+ *   S[i,j] = q_i.k_j + c2p[i, lut[i-j+L-1]] + p2c[j, lut[i-j+L-1]]
+ *   P      = softmax_j( S * scale ) under the factorised padding mask
+ *   out[b,i,h*d:(h+1)*d] = P V
+ * Mask rule: pair (i,j) attended iff mask[b,i] && mask[b,j]; a padded query
+ * row is uniform over all L keys.  [B,H,L,L] is never written to memory.
+ */
+typedef struct DflAttnParams {
+  const void* q;          /* [B,H,L,d] */
+  const void* k;          /* [B,H,L,d] */
+  const void* v;          /* [B,H,L,d] */
+  const void* c2p;        /* [B,H,L,ld_slots] or NULL (term disabled) */
+  const void* p2c;        /* [B,H,L,ld_slots] or NULL (term disabled) */
+  const int32_t* lut;     /* [2L-1]; may be NULL when both terms are disabled */
+  const void* mask;       /* [B,L], mask_elem_size bytes per element, non-zero = keep */
+  void*       out;        /* [B,L,H*d] */
+  int32_t*    status;     /* optional device int32: set non-zero if a bounded wait expired */
+  int32_t batch, heads, seq_len, head_dim;
+  int32_t ld_slots;
+  int32_t mask_elem_size; /* 1, 4 or 8 */
+  float   scale;          /* 1/sqrt(head_dim * (1 + has_c2p + has_p2c)), natural units */
+  int32_t dtype, algo;
+} DflAttnParams;
+DFL_API int dfl_attention_fwd(const DflAttnParams* p, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* DFL_B200_H_ */

@@ -1,0 +1,364 @@
+"""GPU parity tests: every C-ABI entry point against the CPU oracle.
+
+All calls go through ``libdfl_b200.so`` (via the ctypes binding).  Integer
+results must be bit-exact; floating-point results must satisfy
+``helpers.tolerance`` (1e-5 for strict FP32, 2e-3 plus one output rounding
+step for FP16/BF16), always against the fp32 oracle evaluated on the same
+rounded inputs.  The case matrix follows the reference's validation script
+(validation/validate_cuda.py: lengths around tile boundaries, mask patterns
+none/right/left/heavy/all, modes c2p/p2c/both, head dims 32/64/128).
+"""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import ATTENTION_GOLDEN, load_attention_golden
+from helpers import MASK_PATTERNS, assert_close, make_core_case, make_mask, oracle_core, oracle_encoder_forward, plan_for
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32}
+
+
+def _cabi():
+    from disentangled_flash_b200 import _cabi
+
+    return _cabi
+
+
+def algo_code(name):
+    c = _cabi()
+    return {"auto": c.ALGO_AUTO, "simt": c.ALGO_SIMT}[name]
+
+
+def algos_for(dtype_name):
+    # fp32 has a single (IEEE CUDA-core) implementation; 16-bit types have the
+    # tcgen05 kernels ("auto") and the CUDA-core cross-check path ("simt").
+    return ("auto",) if dtype_name == "fp32" else ("auto", "simt")
+
+
+DTYPE_ALGO = [(d, a) for d in DTYPES for a in algos_for(d)]
+dev = "cuda"
+
+
+# ------------------------------------------------------------------ index builder
+POSITION_CONFIGS = {"b256_m512": (256, 512, 256), "b256_m2048": (256, 2048, 256), "b32_m64": (32, 64, 32),
+                    "nobucket_m512": (-1, 512, 512), "nobucket_m64": (0, 64, 64)}
+LUT_LENGTHS = (1, 2, 3, 16, 31, 32, 33, 63, 64, 65, 127, 128, 129, 255, 256, 257, 384, 511, 512, 513, 1024, 2048)
+
+
+@pytest.mark.parametrize("name", sorted(POSITION_CONFIGS))
+def test_position_lut_bit_exact(name, position_golden):
+    buckets, max_pos, span = POSITION_CONFIGS[name]
+    for length in LUT_LENGTHS:
+        active, lut = _cabi().build_position_lut(length, buckets, max_pos, span, True, torch.device(dev))
+        want = oracle.compact_position_plan(length, position_buckets=buckets, max_relative_positions=max_pos,
+                                            position_embedding_size=span)
+        assert lut.dtype == torch.int32 and active.dtype == torch.int64
+        assert np.array_equal(lut.cpu().numpy(), want.delta_to_local), (name, length)
+        assert np.array_equal(active.cpu().numpy(), want.active_slots), (name, length)
+        assert np.array_equal(lut.cpu().numpy(), position_golden[f"{name}/L{length}/lut"])
+        assert np.array_equal(active.cpu().numpy(), position_golden[f"{name}/L{length}/active"])
+
+
+def test_position_lut_every_length_to_600_and_odd_configs():
+    for buckets, max_pos in ((256, 512), (64, 1024), (16, 40), (128, 300)):
+        span = buckets
+        for length in list(range(1, 600, 7)) + [4096]:
+            active, lut = _cabi().build_position_lut(length, buckets, max_pos, span, True, torch.device(dev))
+            want = oracle.compact_position_plan(length, position_buckets=buckets, max_relative_positions=max_pos,
+                                                position_embedding_size=span)
+            assert np.array_equal(lut.cpu().numpy(), want.delta_to_local), (buckets, max_pos, length)
+            assert np.array_equal(active.cpu().numpy(), want.active_slots), (buckets, max_pos, length)
+
+
+def test_position_lut_without_bias_is_zero():
+    active, lut = _cabi().build_position_lut(9, 256, 512, 256, False, torch.device(dev))
+    assert active.numel() == 0 and not lut.any().item() and lut.numel() == 17
+
+
+def test_plan_cache_reference_pins():
+    # reference tests/test_position.py:6-16
+    import disentangled_flash_b200 as df
+
+    cache = df.SharedPositionPlanCache(position_buckets=256, max_relative_positions=512, position_embedding_size=256)
+    plan = cache.compact(65, torch.device(dev))
+    assert plan.delta_to_local.shape == (129,) and plan.active_slots.ndim == 1 and plan.active_slots.numel() <= 129
+    assert cache.compact(65, torch.device(dev)) is plan
+
+
+# ------------------------------------------------------------------ projections
+@pytest.mark.parametrize("dtype_name,algo", DTYPE_ALGO)
+@pytest.mark.parametrize("shape", [(2, 8, 64, 1, 64), (2, 33, 96, 3, 32), (3, 130, 256, 2, 128), (4, 128, 768, 12, 64)])
+def test_qkv_projection(dtype_name, algo, shape):
+    batch, length, hidden, heads, d = shape
+    dtype = DTYPES[dtype_name]
+    gen = torch.Generator().manual_seed(hash(shape) % 1000)
+    x = torch.randn(batch, length, hidden, generator=gen).to(dtype)
+    ws = [torch.randn(heads * d, hidden, generator=gen).mul_(0.05).to(dtype) for _ in range(3)]
+    bs = [torch.randn(heads * d, generator=gen).mul_(0.1).to(dtype) for _ in range(3)]
+    w, b = oracle.fuse_qkv(*ws, *bs)
+    ref = torch.nn.functional.linear(x.float(), w.float(), b.float()).split(heads * d, dim=-1)
+    outs = _cabi().linear_heads(x.to(dev), w.to(dev), b.to(dev), n_out=3, heads=heads, head_dim=d,
+                                rows_per_seq=length, algo=algo_code(algo))
+    for got, want in zip(outs, ref):
+        assert got.shape == (batch, heads, length, d)
+        assert_close(got, oracle.split_heads(want, heads), dtype, f"qkv {shape} {dtype_name} {algo}")
+    # without bias (reference: bias only if all three projections have one)
+    outs = _cabi().linear_heads(x.to(dev), w.to(dev), None, n_out=3, heads=heads, head_dim=d, rows_per_seq=length,
+                                algo=algo_code(algo))
+    ref = torch.nn.functional.linear(x.float(), w.float()).split(heads * d, dim=-1)
+    assert_close(outs[2], oracle.split_heads(ref[2], heads), dtype, "qkv no-bias")
+
+
+@pytest.mark.parametrize("dtype_name,algo", DTYPE_ALGO)
+def test_relative_projection_and_slot_gather(dtype_name, algo):
+    dtype = DTYPES[dtype_name]
+    heads, d, hidden, span = 4, 64, 256, 256
+    gen = torch.Generator().manual_seed(5)
+    rel = torch.randn(2 * span, hidden, generator=gen).to(dtype)
+    w = torch.randn(heads * d, hidden, generator=gen).mul_(0.05).to(dtype)
+    b = torch.randn(heads * d, generator=gen).mul_(0.1).to(dtype)
+    want = oracle.project_positions(rel.float(), w.float(), b.float(), heads, span)
+    (got,) = _cabi().linear_heads(rel.to(dev), w.to(dev), b.to(dev), n_out=1, heads=heads, head_dim=d,
+                                  rows_per_seq=2 * span, algo=algo_code(algo))
+    assert got.shape == (1, heads, 2 * span, d)
+    assert_close(got[0], want, dtype, "relative projection")
+    plan, _ = plan_for(200)
+    active = torch.from_numpy(plan.active_slots).to(dev)
+    pruned = _cabi().gather_slots(got[0].contiguous(), active)
+    assert torch.equal(pruned.cpu(), got[0].cpu()[:, plan.active_slots])
+
+
+@pytest.mark.parametrize("dtype_name,algo", DTYPE_ALGO)
+@pytest.mark.parametrize("shape", [(2, 2, 33, 32), (2, 3, 130, 64), (1, 2, 512, 128), (2, 12, 256, 64)])
+def test_position_scores(dtype_name, algo, shape):
+    batch, heads, length, d = shape
+    dtype = DTYPES[dtype_name]
+    case = make_core_case(batch, heads, length, d, dtype, seed=length + d)
+    c2p, p2c, ld = _cabi().pos_scores(case["q"].to(dev), case["k"].to(dev), case["pos_key"].to(dev),
+                                      case["pos_query"].to(dev), algo=algo_code(algo))
+    n_active = case["pos_key"].shape[1]
+    assert ld % 8 == 0 and ld >= n_active and c2p.shape == (batch, heads, length, ld)
+    want_c2p = torch.matmul(case["q"].float(), case["pos_key"].float().transpose(-1, -2))
+    want_p2c = torch.matmul(case["k"].float(), case["pos_query"].float().transpose(-1, -2))
+    # scores of magnitude ~sqrt(d): the output rounding term of the tolerance dominates for 16-bit types
+    assert_close(c2p[..., :n_active], want_c2p, dtype, "c2p")
+    assert_close(p2c[..., :n_active], want_p2c, dtype, "p2c")
+    if ld > n_active:
+        assert not c2p[..., n_active:].any().item() and not p2c[..., n_active:].any().item()
+
+
+# ------------------------------------------------------------------ fused attention
+def run_core(case, algo, status=None):
+    c = _cabi()
+    to = lambda t: None if t is None else t.to(dev)  # noqa: E731
+    q, k = to(case["q"]), to(case["k"])
+    c2p = p2c = None
+    ld = 0
+    if case["pos_key"] is not None or case["pos_query"] is not None:
+        c2p, p2c, ld = c.pos_scores(q if case["pos_key"] is not None else None,
+                                    k if case["pos_query"] is not None else None,
+                                    to(case["pos_key"]), to(case["pos_query"]), algo=algo_code(algo))
+    return c.attention_fwd(q, k, to(case["v"]), c2p, p2c, to(case["lut"]), to(case["mask"]), case["scale"],
+                           ld_slots=ld, algo=algo_code(algo), status=status)
+
+
+CORE_LENGTHS = (1, 2, 31, 32, 33, 63, 64, 65, 127, 128, 129, 255, 256, 257, 511, 512, 513)
+
+
+@pytest.mark.parametrize("dtype_name,algo", DTYPE_ALGO)
+@pytest.mark.parametrize("d", (32, 64, 128))
+def test_attention_lengths_around_tile_boundaries(dtype_name, algo, d):
+    dtype = DTYPES[dtype_name]
+    heads = {32: 3, 64: 2, 128: 1}[d]
+    for length in CORE_LENGTHS:
+        case = make_core_case(2, heads, length, d, dtype, seed=1000 + length, mask="right")
+        got = run_core(case, algo)
+        assert_close(got, oracle_core(case), dtype, f"L={length} d={d} {dtype_name} {algo}")
+
+
+@pytest.mark.parametrize("dtype_name,algo", DTYPE_ALGO)
+@pytest.mark.parametrize("mask", MASK_PATTERNS)
+@pytest.mark.parametrize("mode", ("both", "c2p", "p2c", "none"))
+def test_attention_masks_and_modes(dtype_name, algo, mask, mode):
+    dtype = DTYPES[dtype_name]
+    for length, d in ((65, 64), (200, 32)):
+        case = make_core_case(2, 2, length, d, dtype, seed=7 + length, mask=mask, mode=mode)
+        got = run_core(case, algo)
+        assert_close(got, oracle_core(case), dtype, f"mask={mask} mode={mode} L={length}")
+
+
+@pytest.mark.parametrize("dtype_name,algo", DTYPE_ALGO)
+def test_attention_long_and_small_bucket_tables(dtype_name, algo):
+    dtype = DTYPES[dtype_name]
+    # L beyond the bucket table (active slots saturate at 2*span) and a tiny table (long log-bucket runs)
+    for length, buckets, max_pos in ((1024, 256, 512), (300, 32, 64), (2048, 256, 2048)):
+        batch = 1
+        case = make_core_case(batch, 2, length, 64, dtype, seed=length, buckets=buckets, max_pos=max_pos,
+                              mask="left")
+        got = run_core(case, algo)
+        assert_close(got, oracle_core(case), dtype, f"L={length} buckets={buckets}")
+
+
+@pytest.mark.parametrize("dtype_name,algo", DTYPE_ALGO)
+def test_attention_mask_element_types(dtype_name, algo):
+    dtype = DTYPES[dtype_name]
+    case = make_core_case(2, 2, 70, 64, dtype, seed=3, mask="heavy")
+    want = oracle_core(case)
+    for mask_dtype in (torch.bool, torch.uint8, torch.int32, torch.int64):
+        alt = dict(case, mask=case["mask"].to(mask_dtype))
+        assert_close(run_core(alt, algo), want, dtype, f"mask dtype {mask_dtype}")
+
+
+@pytest.mark.parametrize("dtype_name,algo", DTYPE_ALGO)
+def test_padded_query_rows_are_uniform_and_runs_are_deterministic(dtype_name, algo):
+    dtype = DTYPES[dtype_name]
+    case = make_core_case(3, 2, 190, 64, dtype, seed=11, mask="all")
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    a = run_core(case, algo, status)
+    b = run_core(case, algo, status)
+    assert torch.equal(a, b), "two identical launches differ (race)"
+    assert status.item() == 0
+    v = case["v"].float()  # [B,H,L,d]
+    mean_v = v.mean(dim=2).reshape(3, 1, -1).expand(3, 190, -1)
+    padded = ~case["mask"]
+    assert_close(a.cpu()[padded], mean_v[padded], dtype, "padded rows = mean(V)")
+
+
+# ------------------------------------------------------------------ module level (golden fixtures)
+def build_module(g, dtype):
+    import disentangled_flash_b200 as df
+
+    c = g["case"]
+    cfg = df.DebertaAttentionConfig(
+        hidden_size=c["hidden"], num_attention_heads=c["heads"], attention_head_size=c["d"],
+        relative_attention=bool(c["rel"]), max_relative_positions=-1, max_position_embeddings=c["max_pos"],
+        position_buckets=c["buckets"], share_att_key=bool(c["share"]), pos_att_type=g["types"], norm_rel_ebd="none",
+    )
+    module = df.DisentangledFlashAttention(cfg)
+    module.load_state_dict(g["params"], strict=True)
+    return module.to(device=dev, dtype=dtype).eval()
+
+
+@pytest.mark.parametrize("name", ATTENTION_GOLDEN)
+def test_module_matches_reference_golden_fp32(name):
+    g = load_attention_golden(name)
+    module = build_module(g, torch.float32)
+    with torch.no_grad():
+        out, none = module(g["hidden_states"].to(dev), g["mask"].to(dev), rel_embeddings=g["rel_embeddings"].to(dev))
+    assert none is None
+    # golden tensors come from the reference's own fp32 backends
+    assert_close(out, g["ctx_original"], torch.float32, f"{name} vs original")
+    assert_close(out, g["ctx_torch"], torch.float32, f"{name} vs torch backend")
+
+
+@pytest.mark.parametrize("name", ATTENTION_GOLDEN)
+@pytest.mark.parametrize("dtype_name", ("fp16", "bf16"))
+def test_module_matches_oracle_low_precision(name, dtype_name):
+    from test_oracle_attention import run_oracle
+
+    dtype = DTYPES[dtype_name]
+    g = load_attention_golden(name)
+    # oracle on the rounded parameters and inputs, evaluated in fp32
+    g16 = dict(g, params={k: v.to(dtype).float() for k, v in g["params"].items()},
+               hidden_states=g["hidden_states"].to(dtype).float(), rel_embeddings=g["rel_embeddings"].to(dtype).float())
+    want = run_oracle(g16)
+    module = build_module(g, dtype)
+    with torch.no_grad():
+        out, _ = module(g["hidden_states"].to(dev, dtype), g["mask"].to(dev), rel_embeddings=g["rel_embeddings"].to(dev, dtype))
+    # inputs of magnitude ~1 with std-0.3 weights: Q/K/V and the score GEMM outputs are themselves rounded to
+    # 16 bits on the way (as in the reference), which the tolerance's rounding term does not cover; allow 4x.
+    err = (out.float().cpu() - want).abs()
+    bound = 4 * (2e-3 + want.abs() * (2.0 ** -11 if dtype == torch.float16 else 2.0 ** -8))
+    assert (err <= bound).all(), f"{name} {dtype_name}: max err {err.max().item():.3e}"
+
+
+def test_reference_fused_qkv_pins():
+    # reference tests/test_fused_qkv.py:7-30 (shapes differ only in being head-major)
+    import disentangled_flash_b200 as df
+
+    cfg = df.DebertaAttentionConfig(hidden_size=64, num_attention_heads=1, attention_head_size=64,
+                                    relative_attention=True, max_relative_positions=64, max_position_embeddings=64,
+                                    position_buckets=32, share_att_key=True, pos_att_type=("c2p", "p2c"),
+                                    norm_rel_ebd="none")
+    module = df.DisentangledFlashAttention(cfg).to(dev).eval()
+    module.prepare_for_inference(torch.randn(64, 64, device=dev))
+    assert module._cached_qkv_weight.shape == (192, 64)
+    with torch.inference_mode():
+        q, k, v = module._project_qkv(torch.randn(2, 8, 64, device=dev))
+    assert q.shape == k.shape == v.shape == (2, 1, 8, 64)
+
+
+# ------------------------------------------------------------------ encoder level
+@pytest.mark.parametrize("dtype_name", ("fp32", "fp16", "bf16"))
+def test_encoder_wrapper_matches_oracle_encoder(dtype_name):
+    import copy
+
+    import disentangled_flash_b200 as df
+    from disentangled_flash_b200 import hf_modules
+
+    dtype = DTYPES[dtype_name]
+    cfg = df.DebertaAttentionConfig(hidden_size=128, num_attention_heads=2, attention_head_size=64,
+                                    num_hidden_layers=3, intermediate_size=256, max_position_embeddings=512,
+                                    position_buckets=256, norm_rel_ebd="layer_norm", conv_kernel_size=3,
+                                    hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    cpu = hf_modules.Backbone(cfg, vocab_size=100).eval()
+    hf_modules.initialize_parameters(cpu, seed=17, std=0.05)
+    gpu = copy.deepcopy(cpu).to(device=dev, dtype=dtype).eval()
+    if dtype != torch.float32:  # the oracle sees the same rounded parameters
+        cpu = copy.deepcopy(gpu).to(device="cpu", dtype=torch.float32).eval()
+    keys_before = set(gpu.state_dict())
+    df.optimize_deberta(gpu, sequence_lengths=[48, 130])
+    assert set(gpu.state_dict()) == keys_before
+
+    gen = torch.Generator().manual_seed(3)
+    for length in (130, 48):
+        mask = make_mask("right", 3, length, gen)
+        hidden = torch.randn(3, length, 128, generator=gen).to(dtype)
+        want = oracle_encoder_forward(cpu, cfg, hidden.float(), mask)
+        gpu.encoder.activate_shape(length)
+        with torch.inference_mode():
+            out = gpu.encoder(hidden.to(dev), mask.to(dev))
+        assert len(out.hidden_states) == 4 and out[0] is out.last_hidden_state
+        got = out.last_hidden_state.float().cpu()
+        valid = mask  # padded positions are zeroed by the conv branch and renormalised later; compare all
+        tol = 2e-4 if dtype == torch.float32 else (3e-2 if dtype == torch.float16 else 1.5e-1)
+        assert (got - want).abs().max().item() <= tol, (dtype_name, length, (got - want).abs().max().item())
+        del valid
+    with torch.inference_mode(), pytest.raises(ValueError, match="activate_shape"):
+        gpu.encoder(torch.zeros(1, 64, 128, device=dev, dtype=dtype), torch.ones(1, 64, device=dev, dtype=torch.bool))
+
+
+def test_module_rejections_on_gpu():
+    import disentangled_flash_b200 as df
+
+    cfg = df.DebertaAttentionConfig(hidden_size=64, num_attention_heads=2, attention_head_size=32,
+                                    max_position_embeddings=64, position_buckets=32, norm_rel_ebd="none")
+    module = df.DisentangledFlashAttention(cfg).to(dev).half().eval()
+    rel = torch.randn(64, 64, device=dev, dtype=torch.float16)
+    hidden = torch.randn(2, 10, 64, device=dev, dtype=torch.float16)
+    mask = torch.ones(2, 10, dtype=torch.bool, device=dev)
+    with torch.no_grad():
+        module.prepare_for_inference(rel)
+        plan = module.prepare_shape(10)
+        with pytest.raises(ValueError, match="prepared length"):
+            module.forward_prepared(hidden[:, :9], mask[:, :9], plan)
+        with pytest.raises(ValueError, match="factorized"):
+            module.forward_prepared(hidden, mask[:, None, :], plan)
+        with pytest.raises(TypeError):
+            module.forward_prepared(hidden.double(), mask, plan)
+        with pytest.raises(TypeError, match="dtype"):
+            module.forward_prepared(hidden.float(), mask, plan)
+        with pytest.raises(ValueError, match="output_attentions"):
+            module(hidden, mask, output_attentions=True)
+        out, _ = module.forward_prepared(hidden, mask, plan)
+        assert out.shape == (2, 10, 64) and out.dtype == torch.float16
+    with pytest.raises(RuntimeError, match="no_grad"):
+        module.forward_prepared(hidden, mask, plan)
+    module.float()  # _apply drops every derived cache
+    assert module._cached_qkv_weight is None
