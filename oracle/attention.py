@@ -71,8 +71,15 @@ def attention_core(
     mask: torch.Tensor,
     *,
     scale_factor: int | None = None,
+    score_dtype: torch.dtype | None = None,
 ) -> torch.Tensor:
     """Scores + C2P/P2C gathers + mask + softmax + PV.
+
+    ``score_dtype``: when the model runs in FP16/BF16 the reference's two
+    position-score GEMMs return tensors of that dtype (``kernel.py:577,583``),
+    i.e. every C2P/P2C score is rounded to 16 bits before it is added to the
+    fp32 content score.  Passing the dtype here reproduces that one rounding
+    while everything else stays in the precision of ``q``.
 
     ``q, k, v``: ``[B, H, L, d]``; ``pos_key``/``pos_query``: ``[H, A, d]``
     already pruned to the active slots (or ``None`` when the term is off);
@@ -99,10 +106,16 @@ def attention_core(
         pair = lut[idx[:, None] - idx[None, :] + length - 1]
         pair = pair.view(1, 1, length, length).expand(bsz, heads, length, length)
     if has_c2p:
-        c2p = torch.matmul(q, pos_key.transpose(-1, -2)) / scale
+        c2p = torch.matmul(q, pos_key.transpose(-1, -2))
+        if score_dtype is not None:
+            c2p = c2p.to(score_dtype).to(q.dtype)
+        c2p = c2p / scale
         scores = scores + torch.gather(c2p, dim=-1, index=pair)
     if has_p2c:
-        p2c = torch.matmul(k, pos_query.transpose(-1, -2)) / scale
+        p2c = torch.matmul(k, pos_query.transpose(-1, -2))
+        if score_dtype is not None:
+            p2c = p2c.to(score_dtype).to(q.dtype)
+        p2c = p2c / scale
         scores = scores + torch.gather(p2c.transpose(-1, -2), dim=-2, index=pair)
 
     keep = mask.to(torch.bool)

@@ -62,18 +62,24 @@ def make_core_case(batch, heads, length, d, dtype, seed, *, mode="both", mask="r
 
 
 def oracle_core(case, compute=torch.float32):
-    """fp32 (or fp64) oracle on the same, already rounded, inputs."""
+    """fp32 (or fp64) oracle on the same, already rounded, inputs.
+
+    For 16-bit cases the C2P/P2C scores are rounded once to the input dtype,
+    as the reference's position-score GEMMs do; nothing else is rounded.
+    """
 
     up = lambda t: None if t is None else t.to(compute)  # noqa: E731
+    in_dtype = case["q"].dtype
     with torch.no_grad():
         return oracle.attention_core(up(case["q"]), up(case["k"]), up(case["v"]), up(case["pos_key"]),
-                                     up(case["pos_query"]), case["plan"].delta_to_local, case["mask"])
+                                     up(case["pos_query"]), case["plan"].delta_to_local, case["mask"],
+                                     score_dtype=None if in_dtype == torch.float32 else in_dtype)
 
 
 def tolerance(dtype: torch.dtype, ref: torch.Tensor) -> torch.Tensor:
     """Element-wise bound used by every floating-point parity test.
 
-    FP32: 1e-5 absolute (the strict-FP32 target).  FP16/BF16: 2e-3 absolute
+    FP32: 1e-5 absolute plus 1e-5 relative (the strict-FP32 target).  FP16/BF16: 2e-3 absolute
     plus one rounding step of the output dtype at the reference magnitude
     (2^-11 relative for FP16, 2^-8 for BF16): an output of magnitude ~1 cannot
     be stored in BF16 to better than 3.9e-3, whatever computes it.
@@ -81,7 +87,9 @@ def tolerance(dtype: torch.dtype, ref: torch.Tensor) -> torch.Tensor:
 
     ref = ref.abs().to(torch.float64)
     if dtype == torch.float32:
-        return torch.full_like(ref, 1e-5) + ref * 2e-6
+        # 1e-5 absolute for outputs up to magnitude 1 (the reference's benchmark regime has |out| << 1);
+        # larger outputs get the same bound relative to their size (fp32 has 24 bits at any magnitude).
+        return torch.full_like(ref, 1e-5) + ref * 1e-5
     ulp = 2.0 ** -11 if dtype == torch.float16 else 2.0 ** -8
     return torch.full_like(ref, 2e-3) + ref * ulp
 

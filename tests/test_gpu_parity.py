@@ -303,6 +303,9 @@ def test_encoder_wrapper_matches_oracle_encoder(dtype_name):
     from disentangled_flash_b200 import hf_modules
 
     dtype = DTYPES[dtype_name]
+    # the PyTorch layers around the attention must not silently use TF32 (cuDNN convolutions do by default)
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
     cfg = df.DebertaAttentionConfig(hidden_size=128, num_attention_heads=2, attention_head_size=64,
                                     num_hidden_layers=3, intermediate_size=256, max_position_embeddings=512,
                                     position_buckets=256, norm_rel_ebd="layer_norm", conv_kernel_size=3,
