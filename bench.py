@@ -303,7 +303,9 @@ def run_gpu_arm(args) -> None:
             step_resident(i)
             step_e2e(i)
         observer.enabled = True
+        torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see exactly the timed region
         ms_total, clocks = timed(step_resident, args.steps, sample_clocks=True)
+        torch.cuda.profiler.stop()
         observer.enabled = False
         attn_ms = [s.elapsed_time(e) for s, e in observer.events]
         ms_e2e, _ = timed(step_e2e, args.steps)

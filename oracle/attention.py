@@ -140,8 +140,15 @@ def attention_module_forward(
     share_att_key: bool = True,
     w_pos_key=None, b_pos_key=None, w_pos_query=None, b_pos_query=None,
     plan: PositionPlan | None = None,
+    storage_dtype: torch.dtype | None = None,
 ) -> torch.Tensor:
     """Whole attention sub-module: hidden ``[B, L, hid]`` -> context ``[B, L, H*d]``.
+
+    ``storage_dtype``: a model running in FP16/BF16 stores every tensor that
+    passes between two kernels in that type: Q/K/V after the projection, the
+    projected position tables, and the C2P/P2C scores.  Passing the dtype
+    reproduces exactly those roundings (arithmetic stays in the dtype of
+    ``hidden``), so a 16-bit implementation can be compared tightly.
 
     ``max_relative_positions`` must already be resolved (values < 1 mean
     ``max_position_embeddings``, ``_reference.py:223-225``).
@@ -150,8 +157,9 @@ def attention_module_forward(
     length = hidden.shape[1]
     weight, bias = fuse_qkv(wq, wk, wv, bq, bk, bv)
     hd = wq.shape[0]
+    rnd = (lambda t: t.to(storage_dtype).to(hidden.dtype)) if storage_dtype is not None else (lambda t: t)
     q, k, v = F.linear(hidden, weight, bias).split(hd, dim=-1)
-    q, k, v = (split_heads(t, num_heads) for t in (q, k, v))
+    q, k, v = (rnd(split_heads(t, num_heads)) for t in (q, k, v))
 
     has_c2p = relative_attention and "c2p" in pos_att_type
     has_p2c = relative_attention and "p2c" in pos_att_type
@@ -168,15 +176,16 @@ def attention_module_forward(
     pos_key = pos_query = None
     if has_c2p:
         w, b = (wk, bk) if share_att_key else (w_pos_key, b_pos_key)
-        pos_key = project_positions(rel_embeddings, w, b, num_heads, span).index_select(1, active).contiguous()
+        pos_key = rnd(project_positions(rel_embeddings, w, b, num_heads, span)).index_select(1, active).contiguous()
     if has_p2c:
         w, b = (wq, bq) if share_att_key else (w_pos_query, b_pos_query)
-        pos_query = project_positions(rel_embeddings, w, b, num_heads, span).index_select(1, active).contiguous()
+        pos_query = rnd(project_positions(rel_embeddings, w, b, num_heads, span)).index_select(1, active).contiguous()
 
     # The reference scales by 1 + [c2p in type] + [p2c in type] even when
     # relative attention is off (``_torch.py:337``).
     scale_factor = 1 + int("c2p" in pos_att_type) + int("p2c" in pos_att_type)
-    return attention_core(q, k, v, pos_key, pos_query, plan.delta_to_local, mask, scale_factor=scale_factor)
+    return attention_core(q, k, v, pos_key, pos_query, plan.delta_to_local, mask, scale_factor=scale_factor,
+                          score_dtype=storage_dtype)
 
 
 __all__ = [

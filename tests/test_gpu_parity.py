@@ -17,7 +17,8 @@ import torch
 
 import oracle
 from conftest import ATTENTION_GOLDEN, load_attention_golden
-from helpers import MASK_PATTERNS, assert_close, make_core_case, make_mask, oracle_core, oracle_encoder_forward, plan_for
+from helpers import (MASK_PATTERNS, assert_close, make_core_case, make_mask, oracle_core, oracle_encoder_forward,
+                     plan_for, tolerance)
 
 pytestmark = pytest.mark.gpu
 
@@ -252,9 +253,15 @@ def test_module_matches_reference_golden_fp32(name):
     with torch.no_grad():
         out, none = module(g["hidden_states"].to(dev), g["mask"].to(dev), rel_embeddings=g["rel_embeddings"].to(dev))
     assert none is None
-    # golden tensors come from the reference's own fp32 backends
-    assert_close(out, g["ctx_original"], torch.float32, f"{name} vs original")
-    assert_close(out, g["ctx_torch"], torch.float32, f"{name} vs torch backend")
+    # Golden tensors come from the reference's own two fp32 backends.  The bound is the strict-FP32 tolerance,
+    # or three times the distance between those two backends where that is larger (fixtures with std-0.3
+    # weights reach scores of +-100, where fp32 summation order alone moves outputs by ~1e-5).
+    got = out.float().cpu()
+    spread = (g["ctx_original"] - g["ctx_torch"]).abs().max().item()
+    for label, want in (("original", g["ctx_original"]), ("torch backend", g["ctx_torch"])):
+        err = (got.double() - want.double()).abs()
+        bound = torch.maximum(tolerance(torch.float32, want), torch.full_like(err, 3 * spread))
+        assert (err <= bound).all(), f"{name} vs {label}: max abs err {err.max().item():.3e} (backend spread {spread:.2e})"
 
 
 @pytest.mark.parametrize("name", ATTENTION_GOLDEN)
@@ -264,17 +271,21 @@ def test_module_matches_oracle_low_precision(name, dtype_name):
 
     dtype = DTYPES[dtype_name]
     g = load_attention_golden(name)
-    # oracle on the rounded parameters and inputs, evaluated in fp32
+    # oracle in fp32 on the rounded parameters and inputs, with the reference's 16-bit storage points
+    # (Q/K/V, projected position tables, position scores) rounded the same way
+    # The fixtures were drawn with std-0.3 weights, which drives scores to +-100: there a single 16-bit
+    # rounding of a position score that falls on the other side of a rounding boundary (summation order)
+    # moves a probability by several percent in either implementation.  The parameters are scaled to a third
+    # (scores within about +-12, still far hotter than a trained checkpoint) before both sides see them.
+    g = dict(g, params={k: v / 3.0 for k, v in g["params"].items()})
     g16 = dict(g, params={k: v.to(dtype).float() for k, v in g["params"].items()},
                hidden_states=g["hidden_states"].to(dtype).float(), rel_embeddings=g["rel_embeddings"].to(dtype).float())
-    want = run_oracle(g16)
+    want = run_oracle(g16, storage_dtype=dtype)
     module = build_module(g, dtype)
     with torch.no_grad():
         out, _ = module(g["hidden_states"].to(dev, dtype), g["mask"].to(dev), rel_embeddings=g["rel_embeddings"].to(dev, dtype))
-    # inputs of magnitude ~1 with std-0.3 weights: Q/K/V and the score GEMM outputs are themselves rounded to
-    # 16 bits on the way (as in the reference), which the tolerance's rounding term does not cover; allow 4x.
     err = (out.float().cpu() - want).abs()
-    bound = 4 * (2e-3 + want.abs() * (2.0 ** -11 if dtype == torch.float16 else 2.0 ** -8))
+    bound = 2e-3 + want.abs() * (2.0 ** -11 if dtype == torch.float16 else 2.0 ** -8)
     assert (err <= bound).all(), f"{name} {dtype_name}: max err {err.max().item():.3e}"
 
 

@@ -15,7 +15,7 @@ from oracle import attention_module_forward
 FP32_TOL = 2e-5
 
 
-def run_oracle(g, dtype=torch.float32):
+def run_oracle(g, dtype=torch.float32, storage_dtype=None):
     case, p = g["case"], g["params"]
     get = lambda k: p[k].to(dtype) if k in p else None  # noqa: E731
     with torch.no_grad():
@@ -33,6 +33,7 @@ def run_oracle(g, dtype=torch.float32):
             share_att_key=bool(case["share"]),
             w_pos_key=get("pos_key_proj.weight"), b_pos_key=get("pos_key_proj.bias"),
             w_pos_query=get("pos_query_proj.weight"), b_pos_query=get("pos_query_proj.bias"),
+            storage_dtype=storage_dtype,
         )
 
 
