@@ -39,6 +39,8 @@ EXPORTED_SYMBOLS = (
     "dfl_gather_slots",
     "dfl_pos_scores",
     "dfl_attention_fwd",
+    "dfl_attention_fwd_static",
+    "dfl_static_scratch_bytes",
 )
 
 
@@ -65,6 +67,16 @@ class DflAttnParams(Structure):
         ("lut", c_void_p), ("mask", c_void_p), ("out", c_void_p), ("status", c_void_p),
         ("batch", c_int32), ("heads", c_int32), ("seq_len", c_int32), ("head_dim", c_int32),
         ("ld_slots", c_int32), ("mask_elem_size", c_int32), ("scale", c_float),
+        ("dtype", c_int32), ("algo", c_int32),
+    ]
+
+
+class DflAttnStaticParams(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("pos_key", c_void_p), ("pos_query", c_void_p),
+        ("lut", c_void_p), ("mask", c_void_p), ("out", c_void_p), ("status", c_void_p),
+        ("batch", c_int32), ("heads", c_int32), ("seq_len", c_int32), ("head_dim", c_int32),
+        ("n_active", c_int32), ("mask_elem_size", c_int32), ("scale", c_float),
         ("dtype", c_int32), ("algo", c_int32),
     ]
 
@@ -130,6 +142,9 @@ def load_library() -> ctypes.CDLL:
     lib.dfl_pos_scores.argtypes = [POINTER(DflPosScoreParams), c_void_p]
     lib.dfl_attention_fwd.restype = c_int
     lib.dfl_attention_fwd.argtypes = [POINTER(DflAttnParams), c_void_p]
+    lib.dfl_attention_fwd_static.restype = c_int
+    lib.dfl_attention_fwd_static.argtypes = [POINTER(DflAttnStaticParams), c_void_p]
+    lib.dfl_static_scratch_bytes.restype = ctypes.c_size_t
     _lib = lib
     return lib
 
@@ -271,4 +286,36 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, c2p: torch.
     p.dtype, p.algo = dtype_code(q.dtype), algo
     with torch.cuda.device(q.device), _observe("dfl_attention_fwd", 1):
         _check(lib.dfl_attention_fwd(ctypes.byref(p), _stream(q.device)), "dfl_attention_fwd")
+    return out
+
+
+def attention_fwd_static(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_key: torch.Tensor | None,
+                         pos_query: torch.Tensor | None, lut: torch.Tensor | None, mask: torch.Tensor, scale: float,
+                         out: torch.Tensor, *, algo: int = ALGO_AUTO) -> torch.Tensor:
+    """Score GEMMs + fused attention without any allocation inside the call.
+
+    For callers that cannot allocate device memory where the call is made (a
+    server that owns the device through its own arena, a plug-in inside a
+    host runtime's callback): the C2P/P2C scores stay in a fixed 32 MiB array
+    inside the library instead of caller-allocated buffers, and ``out`` is
+    passed in.  Requests that need more raise ``ValueError``.  Calls share the
+    array, so calls that overlap on the GPU race; the first call per device
+    does one-time set-up and belongs before any stream capture.
+    """
+
+    lib = load_library()
+    for name, t in (("q", q), ("k", k), ("v", v), ("mask", mask), ("out", out)):
+        _require_cuda_contiguous(name, t)
+    bsz, heads, length, d = q.shape
+    if out.shape != (bsz, length, heads * d) or out.dtype != q.dtype:
+        raise ValueError("out must be [B, L, H*d] in the dtype of q")
+    table = pos_key if pos_key is not None else pos_query
+    p = DflAttnStaticParams()
+    p.q, p.k, p.v, p.pos_key, p.pos_query = q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(pos_key), _ptr(pos_query)
+    p.lut, p.mask, p.out, p.status = _ptr(lut), mask.data_ptr(), out.data_ptr(), None
+    p.batch, p.heads, p.seq_len, p.head_dim = bsz, heads, length, d
+    p.n_active = 0 if table is None else table.shape[1]
+    p.mask_elem_size, p.scale, p.dtype, p.algo = mask.element_size(), scale, dtype_code(q.dtype), algo
+    with torch.cuda.device(q.device), _observe("dfl_attention_fwd_static", 3):
+        _check(lib.dfl_attention_fwd_static(ctypes.byref(p), _stream(q.device)), "dfl_attention_fwd_static")
     return out

@@ -15,6 +15,7 @@
 #ifndef DFL_B200_H_
 #define DFL_B200_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #if defined(__GNUC__)
@@ -153,6 +154,47 @@ typedef struct DflAttnParams {
   int32_t dtype, algo;
 } DflAttnParams;
 DFL_API int dfl_attention_fwd(const DflAttnParams* p, void* stream);
+
+/*
+ * Allocation-free variant of dfl_pos_scores followed by dfl_attention_fwd.  It has no counterpart
+ * in the reference (whose launcher allocates with torch.empty on every call).
+ *
+ * Who needs it: callers that cannot allocate device memory at the point of the call, e.g. a server
+ * that gave the whole device to its own arena at start-up, or a plug-in running inside a host
+ * runtime's callback where cudaMalloc (a device-wide synchronisation) is off limits.  The C2P/P2C
+ * score tensors, which the regular path keeps in caller-allocated buffers, live here in a fixed
+ * array inside the library's device image.  The call performs no cudaMalloc/cudaFree and calls no
+ * allocating library routine; inputs and the output are still the caller's.
+ *
+ * Limit: DFL_STATIC_SCRATCH_BYTES (32 MiB), held by every GPU context that loads the library until
+ * it exits.  Needed: (number of enabled terms) * batch*heads*seq_len*ceil8(n_active)*sizeof(element),
+ * each term rounded up to 256 bytes; larger requests return DFL_ERR_TOO_LARGE and touch nothing.
+ *
+ * The first call on each device looks up the array's device address (with that device current) and
+ * performs the kernels' one-time configuration; make that first call before any stream capture.
+ * All calls on a device share the one array and it keeps the last call's scores: every element a
+ * call reads is rewritten by that same call first, so nothing has to be cleared, but two calls whose
+ * kernels overlap on the GPU (different streams, or different host threads) race on it.
+ */
+#define DFL_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+typedef struct DflAttnStaticParams {
+  const void* q;          /* [B,H,L,d] */
+  const void* k;          /* [B,H,L,d] */
+  const void* v;          /* [B,H,L,d] */
+  const void* pos_key;    /* [H,A,d] or NULL (C2P disabled) */
+  const void* pos_query;  /* [H,A,d] or NULL (P2C disabled) */
+  const int32_t* lut;     /* [2L-1]; may be NULL when both terms are disabled */
+  const void* mask;       /* [B,L] */
+  void*       out;        /* [B,L,H*d] */
+  int32_t*    status;     /* optional device int32, as in DflAttnParams */
+  int32_t batch, heads, seq_len, head_dim;
+  int32_t n_active;       /* A */
+  int32_t mask_elem_size; /* 1, 4 or 8 */
+  float   scale;
+  int32_t dtype, algo;
+} DflAttnStaticParams;
+DFL_API int    dfl_attention_fwd_static(const DflAttnStaticParams* p, void* stream);
+DFL_API size_t dfl_static_scratch_bytes(void);
 
 #ifdef __cplusplus
 }
