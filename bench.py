@@ -135,13 +135,15 @@ class LaunchObserver:
         self.enabled = False
         self.launches = 0
         self.events = []
+        self.kernel_name = None
 
     def __call__(self, name: str, n_kernels: int):
         if not self.enabled:
             return None
         self.launches += n_kernels
-        if name != "dfl_attention_fwd":
+        if name not in ("dfl_attention_fwd", "dfl_attention_tables_fwd"):
             return None
+        self.kernel_name = name
         observer = self
 
         class Bracket:
@@ -318,16 +320,23 @@ def run_gpu_arm(args) -> None:
 
     # Roofline of the dominant kernel: the fused attention forward (tensor-core bound by design).
     B, H, L, d = args.batch, WORKLOAD["heads"], WORKLOAD["seq_len"], WORKLOAD["head_dim"]
-    flops_per_launch = 4.0 * B * H * L * L * d  # QK^T + PV; the kernel skips no tile
+    flops_attn = 4.0 * B * H * L * L * d  # QK^T + PV; the kernel skips no tile
+    n_active = int(encoder._active_plans[0].active_slots.numel())
+    in_kernel_scores = observer.kernel_name == "dfl_attention_tables_fwd"
+    # with the relative scores computed in-kernel, their non-redundant GEMM work (2 terms, A active slots)
+    # is part of the launch; window MMAs executed beyond that are not counted
+    flops_pos = 2.0 * 2 * B * H * L * n_active * d if in_kernel_scores else 0.0
+    flops_per_launch = flops_attn + flops_pos
     attn_avg_ms = statistics.mean(attn_ms) if attn_ms else float("nan")
     achieved = flops_per_launch / (attn_avg_ms * 1e-3) / 1e12
     peaks, peak_kind = measured_peaks()
     peak = float(peaks.get("bf16_tflops_sustained") or peaks.get("bf16_tflops"))
-    roofline = {"bound": "tensor", "kernel": "dfl_attention_fwd", "achieved": achieved, "peak": peak,
+    roofline = {"bound": "tensor", "kernel": observer.kernel_name, "achieved": achieved, "peak": peak,
                 "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
                 "peak_source": f"{peak_kind} cuBLAS bf16 sustained (kernel timed inside a long step)",
                 "avg_launch_ms": attn_avg_ms, "launches_timed": len(attn_ms),
-                "algorithmic_flops_per_launch": flops_per_launch}
+                "algorithmic_flops_per_launch": flops_per_launch,
+                "flops_qk_pv": flops_attn, "flops_position_scores": flops_pos}
 
     checks = sharding.gather_for_check(checksum)  # NCCL only here, after timing, for checking
     if rank == 0:

@@ -41,6 +41,8 @@ EXPORTED_SYMBOLS = (
     "dfl_attention_fwd",
     "dfl_attention_fwd_static",
     "dfl_static_scratch_bytes",
+    "dfl_attention_tables_supported",
+    "dfl_attention_tables_fwd",
 )
 
 
@@ -71,7 +73,7 @@ class DflAttnParams(Structure):
     ]
 
 
-class DflAttnStaticParams(Structure):
+class DflAttnTablesParams(Structure):
     _fields_ = [
         ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("pos_key", c_void_p), ("pos_query", c_void_p),
         ("lut", c_void_p), ("mask", c_void_p), ("out", c_void_p), ("status", c_void_p),
@@ -143,8 +145,12 @@ def load_library() -> ctypes.CDLL:
     lib.dfl_attention_fwd.restype = c_int
     lib.dfl_attention_fwd.argtypes = [POINTER(DflAttnParams), c_void_p]
     lib.dfl_attention_fwd_static.restype = c_int
-    lib.dfl_attention_fwd_static.argtypes = [POINTER(DflAttnStaticParams), c_void_p]
+    lib.dfl_attention_fwd_static.argtypes = [POINTER(DflAttnTablesParams), c_void_p]
     lib.dfl_static_scratch_bytes.restype = ctypes.c_size_t
+    lib.dfl_attention_tables_supported.restype = c_int
+    lib.dfl_attention_tables_supported.argtypes = [POINTER(DflAttnTablesParams)]
+    lib.dfl_attention_tables_fwd.restype = c_int
+    lib.dfl_attention_tables_fwd.argtypes = [POINTER(DflAttnTablesParams), c_void_p]
     _lib = lib
     return lib
 
@@ -289,6 +295,22 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, c2p: torch.
     return out
 
 
+def _tables_params(q, k, v, pos_key, pos_query, lut, mask, scale, out, algo, status=None) -> DflAttnTablesParams:
+    bsz, heads, length, d = q.shape
+    if out.shape != (bsz, length, heads * d) or out.dtype != q.dtype:
+        raise ValueError("out must be [B, L, H*d] in the dtype of q")
+    if mask.element_size() not in (1, 4, 8) or mask.dtype.is_floating_point:
+        raise TypeError("mask must be a bool or integer tensor")
+    table = pos_key if pos_key is not None else pos_query
+    p = DflAttnTablesParams()
+    p.q, p.k, p.v, p.pos_key, p.pos_query = q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(pos_key), _ptr(pos_query)
+    p.lut, p.mask, p.out, p.status = _ptr(lut), mask.data_ptr(), out.data_ptr(), _ptr(status)
+    p.batch, p.heads, p.seq_len, p.head_dim = bsz, heads, length, d
+    p.n_active = 0 if table is None else table.shape[1]
+    p.mask_elem_size, p.scale, p.dtype, p.algo = mask.element_size(), scale, dtype_code(q.dtype), algo
+    return p
+
+
 def attention_fwd_static(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_key: torch.Tensor | None,
                          pos_query: torch.Tensor | None, lut: torch.Tensor | None, mask: torch.Tensor, scale: float,
                          out: torch.Tensor, *, algo: int = ALGO_AUTO) -> torch.Tensor:
@@ -306,16 +328,37 @@ def attention_fwd_static(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_
     lib = load_library()
     for name, t in (("q", q), ("k", k), ("v", v), ("mask", mask), ("out", out)):
         _require_cuda_contiguous(name, t)
-    bsz, heads, length, d = q.shape
-    if out.shape != (bsz, length, heads * d) or out.dtype != q.dtype:
-        raise ValueError("out must be [B, L, H*d] in the dtype of q")
-    table = pos_key if pos_key is not None else pos_query
-    p = DflAttnStaticParams()
-    p.q, p.k, p.v, p.pos_key, p.pos_query = q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(pos_key), _ptr(pos_query)
-    p.lut, p.mask, p.out, p.status = _ptr(lut), mask.data_ptr(), out.data_ptr(), None
-    p.batch, p.heads, p.seq_len, p.head_dim = bsz, heads, length, d
-    p.n_active = 0 if table is None else table.shape[1]
-    p.mask_elem_size, p.scale, p.dtype, p.algo = mask.element_size(), scale, dtype_code(q.dtype), algo
+    p = _tables_params(q, k, v, pos_key, pos_query, lut, mask, scale, out, algo)
     with torch.cuda.device(q.device), _observe("dfl_attention_fwd_static", 3):
         _check(lib.dfl_attention_fwd_static(ctypes.byref(p), _stream(q.device)), "dfl_attention_fwd_static")
+    return out
+
+
+def attention_tables_supported(q: torch.Tensor, pos_key: torch.Tensor | None, pos_query: torch.Tensor | None,
+                               algo: int = ALGO_AUTO) -> bool:
+    """Whether ``attention_tables_fwd`` (scores computed in-kernel) covers this configuration."""
+
+    table = pos_key if pos_key is not None else pos_query
+    if table is None or algo != ALGO_AUTO:
+        return False
+    p = DflAttnTablesParams()
+    p.pos_key, p.pos_query = _ptr(pos_key), _ptr(pos_query)
+    p.batch, p.heads, p.seq_len, p.head_dim = q.shape
+    p.n_active, p.dtype, p.algo = table.shape[1], dtype_code(q.dtype), algo
+    return bool(load_library().dfl_attention_tables_supported(ctypes.byref(p)))
+
+
+def attention_tables_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_key: torch.Tensor | None,
+                         pos_query: torch.Tensor | None, lut: torch.Tensor, mask: torch.Tensor, scale: float, *,
+                         status: torch.Tensor | None = None) -> torch.Tensor:
+    """Fused attention with the C2P/P2C scores computed inside the kernel from the position tables."""
+
+    lib = load_library()
+    for name, t in (("q", q), ("k", k), ("v", v), ("mask", mask), ("lut", lut)):
+        _require_cuda_contiguous(name, t)
+    bsz, heads, length, d = q.shape
+    out = torch.empty(bsz, length, heads * d, dtype=q.dtype, device=q.device)
+    p = _tables_params(q, k, v, pos_key, pos_query, lut, mask, scale, out, ALGO_AUTO, status)
+    with torch.cuda.device(q.device), _observe("dfl_attention_tables_fwd", 1):
+        _check(lib.dfl_attention_tables_fwd(ctypes.byref(p), _stream(q.device)), "dfl_attention_tables_fwd")
     return out

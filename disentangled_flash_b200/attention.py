@@ -8,12 +8,16 @@ Hugging Face ones (``query_proj``, ``key_proj``, ``value_proj`` and, without
 ``share_att_key``, ``pos_key_proj`` / ``pos_query_proj``) so checkpoints load
 with ``strict=True``.
 
-The hot function is :meth:`forward_prepared`.  It issues exactly three C-ABI
-calls on the current CUDA stream:
+The hot function is :meth:`forward_prepared`.  On the current CUDA stream it
+issues ``dfl_qkv_proj`` (fused QKV projection, written head-major
+``[B,H,L,d]``) followed by
 
-1. ``dfl_qkv_proj``      fused QKV projection, written head-major ``[B,H,L,d]``
-2. ``dfl_pos_scores``    C2P / P2C score GEMMs over the pruned active slots
-3. ``dfl_attention_fwd`` fused QK^T + relative gathers + mask + softmax + PV
+* ``dfl_attention_tables_fwd`` where it applies (FP16/BF16, head dim 32/64):
+  one kernel that computes the C2P/P2C scores over the pruned active slots
+  on the tensor cores and consumes them in place (QK^T + relative gathers +
+  mask + softmax + PV), or otherwise
+* ``dfl_pos_scores`` (the two score GEMMs) and ``dfl_attention_fwd`` (the
+  fused kernel fed with their output), the reference's operator boundary.
 
 There is no PyTorch, Triton or CPU implementation behind them.
 """
@@ -71,6 +75,9 @@ def _attention_forward_op(
         hidden_states, qkv_weight, qkv_bias, n_out=3, heads=num_heads, head_dim=head_dim, rows_per_seq=length,
         algo=algo,
     )
+    if _cabi.attention_tables_supported(query, pos_key, pos_query, algo):
+        # relative scores are produced inside the attention kernel: no [B,H,L,A] tensor in memory
+        return _cabi.attention_tables_fwd(query, key, value, pos_key, pos_query, delta_to_local, attention_mask, scale)
     c2p = p2c = None
     ld_slots = 0
     if pos_key is not None or pos_query is not None:

@@ -1,0 +1,487 @@
+// tcgen05 fused disentangled attention with the relative scores computed in-kernel.
+//
+// Same result as dfl_pos_scores + dfl_attention_fwd (reference: the two torch.matmul calls at
+// src/disentangled_flash/kernel.py:574-585 followed by the Triton kernel kernel.py:137-345), but the
+// C2P and P2C score tensors [B,H,L,A] never exist in global memory: their tiles are produced by
+// tcgen05.mma from the small per-head tables posK / posQ [H,A,d] (L2 resident), rounded to the
+// input type exactly like the separate GEMMs round their output, and parked in shared memory for
+// the softmax threads to gather from.
+//
+// One CTA = 128 query rows of one (batch, head); key tiles of 64.  The slot table lut is monotone
+// with steps 0/1, so the slots a (128 x 64) tile touches form one window [lo, hi] with
+// hi - lo <= 190, and the window moves towards lower slots by at most 64 per key tile.
+//   C2P: c2p[i, s] = q_i . posK[s] depends on the query rows only, so it is kept across key tiles
+//        in a ring of five 64-slot blocks per row; a key tile needs at most one new block
+//        (one 128x64x d MMA, the first tile up to four).
+//   P2C: p2c[j, s] = k_j . posQ[s] is needed for the 64 keys of the tile and the window's slots:
+//        computed transposed, PT[s - lo, j] = posQ[lo + ...] . k_j (one or two 128x64x d MMAs),
+//        so that TMEM lanes are slots and all 128 lanes convert.
+// Ten warps:
+//   warps 0-3  softmax (one thread per query row): S from TMEM, gather c2p from the ring row of the
+//              thread and p2c from PT, then the common softmax tail.
+//   warps 4-7  converters: TMEM -> 16-bit -> shared memory for the C2P blocks and the PT tiles.
+//   warp 8     TMA producer: Q, K/V ring, posK blocks, posQ windows.
+//   warp 9     MMA issuer and TMEM owner: C2P blocks, PT, S = Q K^T, O += P V.
+#include "attention_tc_common.cuh"
+
+namespace dfl {
+
+__device__ int g_attn_fused_status = 0;
+
+namespace {
+
+using attn::BM;
+using attn::BN;
+using attn::Pack2;
+
+constexpr int kThreads = 320;
+constexpr int KV_STAGES = 2;
+constexpr int RING_BLOCKS = 5;
+constexpr int RING_PITCH_H = RING_BLOCKS * 64 + 2;   // halfs per ring row: 644 bytes = 161 words (odd: conflict free)
+constexpr int PT_ROWS = 256;
+constexpr int PT_PITCH_H = BN + 2;                    // halfs per PT row: 132 bytes = 33 words
+constexpr int LUT_LO_PAD = BN;
+constexpr int LUT_HI_PAD = BM;
+
+// TMEM columns (512 allocated; one CTA per SM is guaranteed by its shared-memory footprint)
+constexpr int COL_S = 0;      // 2 x BN
+constexpr int COL_P = 128;    // 2 x BN/2
+constexpr int COL_CNEW = 192; // BN  (one 64-slot C2P block for 128 rows)
+constexpr int COL_PT = 256;   // 2 x BN (slots lo..lo+127 and lo+128..lo+255, 64 keys each)
+constexpr int COL_O = 384;    // D
+constexpr int kTmemCols = 512;
+
+template <int D>
+struct FLayout {
+  static constexpr int kRowBytes = D >= 64 ? 128 : D * 2;
+  static_assert(D <= 64, "in-kernel relative scores are built for head dims 32 and 64");
+  static constexpr int kQ = BM * kRowBytes;            // Q tile; a posQ sub-window has the same shape
+  static constexpr int kK = BN * kRowBytes;            // K tile, V tile, posK block
+  static constexpr int offQ = 0;
+  static constexpr int offKV = offQ + kQ;                      // KV_STAGES x (K, V)
+  static constexpr int offPQ = offKV + KV_STAGES * 2 * kK;     // posQ window operand: 2 sub-windows of 128 slots
+  static constexpr int offPK = offPQ + 2 * kQ;                 // posK block operand
+  static constexpr int offRing = offPK + kK;                   // C2P ring [128][RING_PITCH_H]
+  static constexpr int offPT = offRing + BM * RING_PITCH_H * 2;  // PT staging [256][PT_PITCH_H]
+  static constexpr int offBar = (offPT + PT_ROWS * PT_PITCH_H * 2 + 15) & ~15;
+  static constexpr int kBarBytes = 512;
+  static constexpr int offTables = offBar + kBarBytes;
+  // tables: lutC u16[n_lut], lutP u16[n_lut], win_lo/win_hi int16[n_kt] each, kbits u32[2*n_kt]
+  static int total(int L) {
+    const int n_lut = 2 * L - 1 + LUT_LO_PAD + LUT_HI_PAD;
+    const int n_kt = (L + BN - 1) / BN;
+    return offTables + ((4 * n_lut + 15) & ~15) + ((4 * n_kt + 15) & ~15) + 8 * n_kt + 1024;
+  }
+};
+
+struct FBarriers {
+  uint64_t q_full;
+  uint64_t kv_full[KV_STAGES], kv_empty[KV_STAGES];
+  uint64_t s_full[2], s_free[2], p_full[2];
+  uint64_t o_ready;
+  uint64_t pk_full, pk_empty;        // posK block operand in shared memory
+  uint64_t pq_full, pq_empty;        // posQ window operand in shared memory
+  uint64_t cnew_full, cnew_free;     // C2P block in TMEM
+  uint64_t pt_full, pt_free;         // PT tile in TMEM
+  uint64_t c2p_ready[2];             // ring holds everything tile t needs
+  uint64_t ring_release[2];          // softmax threads finished gathering C2P of tile t
+  uint64_t pt_ready, pt_release;     // PT staging in shared memory
+  uint32_t tmem_base;
+  int abort_flag;
+};
+static_assert(sizeof(FBarriers) <= 512, "barrier block too large");
+
+struct FTables {
+  const uint16_t* lutC;   // ring element index of the slot of each delta
+  const uint16_t* lutP;   // PT_PITCH_H * slot
+  const int16_t* win_lo;  // per key tile: lowest slot touched
+  const int16_t* win_hi;  // per key tile: highest slot touched
+  const uint32_t* kbits;  // key keep-bits
+};
+
+// C2P block jobs of tile t: the first tile brings blocks hi>>6 .. lo>>6, later tiles at most one.
+struct BlockJobs {
+  int first, count;  // blocks first, first-1, ..., first-count+1
+};
+__device__ __forceinline__ BlockJobs c2p_jobs(const FTables& tb, int t) {
+  const int blo = tb.win_lo[t] >> 6;
+  if (t == 0) return {tb.win_hi[0] >> 6, (tb.win_hi[0] >> 6) - blo + 1};
+  const int prev = tb.win_lo[t - 1] >> 6;
+  return {blo, blo < prev ? 1 : 0};
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads, 1)
+attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                       const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_pk,
+                       const __grid_constant__ CUtensorMap tmap_pq, const DflAttnTablesParams p, int* status_word) {
+  using LO = FLayout<D>;
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  FBarriers* bars = reinterpret_cast<FBarriers*>(smem + LO::offBar);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int L = p.seq_len, H = p.heads;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
+  const int i0 = blockIdx.x * BM;
+  const int n_kt = (L + BN - 1) / BN;
+  const bool has_c2p = p.pos_key != nullptr, has_p2c = p.pos_query != nullptr;
+  const int n_lut = 2 * L - 1 + LUT_LO_PAD + LUT_HI_PAD;
+
+  uint16_t* lutC = reinterpret_cast<uint16_t*>(smem + LO::offTables);
+  uint16_t* lutP = lutC + n_lut;
+  int16_t* win_lo = reinterpret_cast<int16_t*>(smem + LO::offTables + ((4 * n_lut + 15) & ~15));
+  int16_t* win_hi = win_lo + n_kt;
+  uint32_t* kbits = reinterpret_cast<uint32_t*>(smem + LO::offTables + ((4 * n_lut + 15) & ~15) + ((4 * n_kt + 15) & ~15));
+  const FTables tb{lutC, lutP, win_lo, win_hi, kbits};
+
+  // ------------------------------------------------------------------ setup
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(&bars->q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      ptx::mbar_init(&bars->kv_full[s], 1);
+      ptx::mbar_init(&bars->kv_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(&bars->s_full[s], 1);
+      ptx::mbar_init(&bars->s_free[s], 128);
+      ptx::mbar_init(&bars->p_full[s], 128);
+      ptx::mbar_init(&bars->c2p_ready[s], 128);
+      ptx::mbar_init(&bars->ring_release[s], 128);
+    }
+    ptx::mbar_init(&bars->o_ready, 1);
+    ptx::mbar_init(&bars->pk_full, 1);
+    ptx::mbar_init(&bars->pk_empty, 1);
+    ptx::mbar_init(&bars->pq_full, 1);
+    ptx::mbar_init(&bars->pq_empty, 1);
+    ptx::mbar_init(&bars->cnew_full, 1);
+    ptx::mbar_init(&bars->cnew_free, 128);
+    ptx::mbar_init(&bars->pt_full, 1);
+    ptx::mbar_init(&bars->pt_free, 128);
+    ptx::mbar_init(&bars->pt_ready, 128);
+    ptx::mbar_init(&bars->pt_release, 128);
+    bars->abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 8 && lane == 0) {
+    ptx::prefetch_tensormap(&tmap_q);
+    ptx::prefetch_tensormap(&tmap_k);
+    ptx::prefetch_tensormap(&tmap_v);
+    ptx::prefetch_tensormap(&tmap_pk);
+    ptx::prefetch_tensormap(&tmap_pq);
+  }
+  if (warp == 9) {
+    ptx::tmem_alloc(&bars->tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  // slot tables, edge-replicated so that out-of-range (i, j) pairs resolve inside the tile's window
+  for (int e = threadIdx.x; e < n_lut; e += kThreads) {
+    int src = e - LUT_LO_PAD;
+    src = src < 0 ? 0 : (src > 2 * L - 2 ? 2 * L - 2 : src);
+    const int s = p.lut[src];
+    lutC[e] = (uint16_t)(((s >> 6) % RING_BLOCKS) * 64 + (s & 63));
+    lutP[e] = (uint16_t)(PT_PITCH_H * s);
+  }
+  for (int t = threadIdx.x; t < n_kt; t += kThreads) {
+    int a = i0 - (t * BN + BN - 1) + (L - 1), z = i0 + (BM - 1) - t * BN + (L - 1);
+    a = a < 0 ? 0 : (a > 2 * L - 2 ? 2 * L - 2 : a);
+    z = z < 0 ? 0 : (z > 2 * L - 2 ? 2 * L - 2 : z);
+    win_lo[t] = (int16_t)p.lut[a];
+    win_hi[t] = (int16_t)p.lut[z];
+  }
+  for (int w = warp; w < 2 * n_kt; w += kThreads / 32) {
+    const int j = w * 32 + lane;
+    const bool keep = j < L && mask_keep(p.mask, p.mask_elem_size, (long long)b * L + j);
+    const uint32_t bits = __ballot_sync(0xffffffffu, keep);
+    if (lane == 0) kbits[w] = bits;
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      bool ok = true;
+      ptx::mbar_arrive_expect_tx(&bars->q_full, (uint32_t)LO::kQ);
+      ptx::tma_load_3d(smem + LO::offQ, &tmap_q, &bars->q_full, 0, i0, bh);
+      uint32_t n_job = 0;
+      for (int t = 0; t < n_kt && ok; ++t) {
+        if (has_c2p) {
+          const BlockJobs jobs = c2p_jobs(tb, t);
+          for (int x = 0; x < jobs.count && ok; ++x, ++n_job) {
+            ok = ptx::mbar_wait(&bars->pk_empty, (n_job & 1u) ^ 1u, abort_flag, status_word, 11);
+            if (!ok) break;
+            ptx::mbar_arrive_expect_tx(&bars->pk_full, (uint32_t)LO::kK);
+            ptx::tma_load_3d(smem + LO::offPK, &tmap_pk, &bars->pk_full, 0, (jobs.first - x) * 64, h);
+          }
+          if (!ok) break;
+        }
+        if (has_p2c) {
+          ok = ptx::mbar_wait(&bars->pq_empty, ((uint32_t)t & 1u) ^ 1u, abort_flag, status_word, 12);
+          if (!ok) break;
+          const int lo = win_lo[t];
+          const bool two = win_hi[t] - lo >= 128;
+          ptx::mbar_arrive_expect_tx(&bars->pq_full, (uint32_t)(two ? 2 * LO::kQ : LO::kQ));
+          ptx::tma_load_3d(smem + LO::offPQ, &tmap_pq, &bars->pq_full, 0, lo, h);
+          if (two) ptx::tma_load_3d(smem + LO::offPQ + LO::kQ, &tmap_pq, &bars->pq_full, 0, lo + 128, h);
+        }
+        const int s = t % KV_STAGES;
+        ok = ptx::mbar_wait(&bars->kv_empty[s], ((uint32_t)(t / KV_STAGES) & 1u) ^ 1u, abort_flag, status_word, 1);
+        if (!ok) break;
+        ptx::mbar_arrive_expect_tx(&bars->kv_full[s], (uint32_t)(2 * LO::kK));
+        unsigned char* kv = smem + LO::offKV + s * 2 * LO::kK;
+        ptx::tma_load_3d(kv, &tmap_k, &bars->kv_full[s], 0, t * BN, bh);
+        ptx::tma_load_3d(kv + LO::kK, &tmap_v, &bars->kv_full[s], 0, t * BN, bh);
+      }
+    }
+  } else if (warp == 9) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr int is_bf16 = __is_same(T, __nv_bfloat16) ? 1 : 0;
+      constexpr uint32_t idesc_64 = ptx::make_idesc_f16(is_bf16, BM, BN, 0, 0);  // 128 x 64, both K-major
+      constexpr uint32_t idesc_pv = ptx::make_idesc_f16(is_bf16, BM, D, 0, 1);   // V is MN-major
+      constexpr uint32_t mode = ptx::swizzle_mode_for_row_bytes(LO::kRowBytes);
+      constexpr uint32_t sbo = 8 * LO::kRowBytes;
+      constexpr int kSteps = LO::kRowBytes / 32;  // K=16 steps over d
+      const uint32_t q_addr = ptx::smem_u32(smem + LO::offQ);
+      const uint32_t pk_addr = ptx::smem_u32(smem + LO::offPK);
+      const uint32_t pq_addr = ptx::smem_u32(smem + LO::offPQ);
+      uint32_t n_job = 0;
+      bool ok = ptx::mbar_wait(&bars->q_full, 0, abort_flag, status_word, 2);
+
+      // D[128 x 64] = A[128 x d] * B[64 x d]^T, both operands K-major tiles in shared memory
+      auto mma_128x64 = [&](uint32_t d_col, uint32_t a_addr, uint32_t b_addr) {
+#pragma unroll
+        for (int k = 0; k < kSteps; ++k) {
+          const uint64_t adesc = ptx::make_smem_desc(a_addr + k * 32, 16, sbo, mode);
+          const uint64_t bdesc = ptx::make_smem_desc(b_addr + k * 32, 16, sbo, mode);
+          ptx::umma_ss_f16(tmem_base + d_col, adesc, bdesc, idesc_64, k != 0 ? 1u : 0u);
+        }
+      };
+
+      // everything tile t needs before its softmax: new C2P blocks, PT, S
+      auto issue_front = [&](int t) -> bool {
+        if (has_c2p) {
+          const BlockJobs jobs = c2p_jobs(tb, t);
+          for (int x = 0; x < jobs.count; ++x, ++n_job) {
+            if (!ptx::mbar_wait(&bars->pk_full, n_job & 1u, abort_flag, status_word, 13)) return false;
+            if (!ptx::mbar_wait(&bars->cnew_free, (n_job & 1u) ^ 1u, abort_flag, status_word, 14)) return false;
+            ptx::tc_fence_after();
+            mma_128x64(COL_CNEW, q_addr, pk_addr);
+            ptx::umma_commit(&bars->pk_empty);
+            ptx::umma_commit(&bars->cnew_full);
+          }
+        }
+        const int s = t % KV_STAGES, sb = t & 1;
+        if (!ptx::mbar_wait(&bars->kv_full[s], (uint32_t)(t / KV_STAGES) & 1u, abort_flag, status_word, 3)) return false;
+        const uint32_t k_addr = ptx::smem_u32(smem + LO::offKV + s * 2 * LO::kK);
+        if (has_p2c) {
+          if (!ptx::mbar_wait(&bars->pq_full, (uint32_t)t & 1u, abort_flag, status_word, 15)) return false;
+          if (!ptx::mbar_wait(&bars->pt_free, ((uint32_t)t & 1u) ^ 1u, abort_flag, status_word, 16)) return false;
+          ptx::tc_fence_after();
+          mma_128x64(COL_PT, pq_addr, k_addr);
+          if (win_hi[t] - win_lo[t] >= 128) mma_128x64(COL_PT + BN, pq_addr + LO::kQ, k_addr);
+          ptx::umma_commit(&bars->pq_empty);
+          ptx::umma_commit(&bars->pt_full);
+        }
+        if (!ptx::mbar_wait(&bars->s_free[sb], ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag, status_word, 4)) return false;
+        ptx::tc_fence_after();
+        mma_128x64(COL_S + sb * BN, q_addr, k_addr);
+        ptx::umma_commit(&bars->s_full[sb]);
+        return true;
+      };
+
+      if (ok) ok = issue_front(0);
+      for (int t = 0; t < n_kt && ok; ++t) {
+        if (t + 1 < n_kt) ok = issue_front(t + 1);
+        if (!ok) break;
+        const int s = t % KV_STAGES, sb = t & 1;
+        ok = ptx::mbar_wait(&bars->p_full[sb], (uint32_t)(t >> 1) & 1u, abort_flag, status_word, 5);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        const uint32_t v_addr = ptx::smem_u32(smem + LO::offKV + s * 2 * LO::kK + LO::kK);
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint64_t bdesc = ptx::make_smem_desc(v_addr + kk * 16 * LO::kRowBytes, LO::kK, sbo, mode);
+          ptx::umma_ts_f16(tmem_base + COL_O, tmem_base + COL_P + sb * (BN / 2) + kk * 8, bdesc, idesc_pv,
+                           (t | kk) != 0 ? 1u : 0u);
+        }
+        ptx::umma_commit(&bars->kv_empty[s]);
+        ptx::umma_commit(&bars->o_ready);
+      }
+    }
+  } else if (warp >= 4) {
+    // -------------------------------------------------------------- converters
+    // Thread (quarter q = warp & 3, lane) owns TMEM lane 32q + lane: a query row for C2P blocks,
+    // a slot (relative to the window start) for PT tiles.
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    unsigned char* ring_row = smem + LO::offRing + row * (RING_PITCH_H * 2);
+    unsigned char* pt_base = smem + LO::offPT;
+    uint32_t n_job = 0;
+    bool ok = true;
+
+    // 64 fp32 columns at t_src -> 64 16-bit values at dst (4-byte aligned), rounded like a GEMM epilogue
+    auto convert_64 = [&](uint32_t t_src, unsigned char* dst) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t raw[32];
+        ptx::tmem_ld32(t_src + half * 32, raw);
+        ptx::tmem_wait_ld();
+#pragma unroll
+        for (int x = 0; x < 32; x += 2)
+          *reinterpret_cast<uint32_t*>(dst + half * 64 + x * 2) =
+              Pack2<T>::pack(__uint_as_float(raw[x]), __uint_as_float(raw[x + 1]));
+      }
+    };
+
+    for (int t = 0; t < n_kt && ok; ++t) {
+      if (has_c2p) {
+        const BlockJobs jobs = c2p_jobs(tb, t);
+        // The ring position a new block overwrites was last needed by tile t-2.  The wait is taken even
+        // when tile t brings no block: it keeps this role at most two tiles ahead of the softmax, which the
+        // two-phase c2p_ready barriers rely on.
+        ok = ptx::mbar_wait(&bars->ring_release[t & 1], ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag, status_word, 17);
+        if (!ok) break;
+        for (int x = 0; x < jobs.count && ok; ++x, ++n_job) {
+          ok = ptx::mbar_wait(&bars->cnew_full, n_job & 1u, abort_flag, status_word, 18);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          const int blk = jobs.first - x;
+          convert_64(tmem_base + lane_base + COL_CNEW, ring_row + (blk % RING_BLOCKS) * 128);
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(&bars->cnew_free);
+        }
+        if (!ok) break;
+        ptx::mbar_arrive(&bars->c2p_ready[t & 1]);
+      }
+      if (has_p2c) {
+        ok = ptx::mbar_wait(&bars->pt_full, (uint32_t)t & 1u, abort_flag, status_word, 19);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        // the staging tile is single-buffered: tile t-1 must have been gathered
+        ok = ptx::mbar_wait(&bars->pt_release, ((uint32_t)t & 1u) ^ 1u, abort_flag, status_word, 20);
+        if (!ok) break;
+        convert_64(tmem_base + lane_base + COL_PT, pt_base + row * (PT_PITCH_H * 2));
+        if (win_hi[t] - win_lo[t] >= 128)
+          convert_64(tmem_base + lane_base + COL_PT + BN, pt_base + (128 + row) * (PT_PITCH_H * 2));
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(&bars->pt_free);
+        ptx::mbar_arrive(&bars->pt_ready);
+      }
+    }
+  } else {
+    // ----------------------------------------------------------------- softmax
+    const int r = warp * 32 + lane;
+    const int i = i0 + r;
+    const bool row_ok = i < L;
+    const bool q_keep = row_ok && mask_keep(p.mask, p.mask_elem_size, (long long)b * L + i);
+    const float cscale = p.scale * 1.4426950408889634f;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t t_o = tmem_base + lane_base + COL_O;
+    const uint16_t* ring_row = reinterpret_cast<const uint16_t*>(smem + LO::offRing) + r * RING_PITCH_H;
+    const uint16_t* pt16 = reinterpret_cast<const uint16_t*>(smem + LO::offPT);
+    attn::RowState st;
+    bool ok = true;
+
+    for (int t = 0; t < n_kt && ok; ++t) {
+      const int sb = t & 1, j0 = t * BN;
+      ok = ptx::mbar_wait(&bars->s_full[sb], (uint32_t)(t >> 1) & 1u, abort_flag, status_word, 7);
+      if (!ok) break;
+      ptx::tc_fence_after();
+      float s[BN];
+      attn::load_scores(tmem_base + lane_base + COL_S + sb * BN, s);
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(&bars->s_free[sb]);
+
+      const int e0 = LUT_LO_PAD + i - j0 + (L - 1);  // table index of pair (i, j0); pair (i, j0+jj) is e0 - jj
+      if (has_c2p) {
+        ok = ptx::mbar_wait(&bars->c2p_ready[sb], (uint32_t)(t >> 1) & 1u, abort_flag, status_word, 8);
+        if (!ok) break;
+        const uint16_t* lc = lutC + e0;
+#pragma unroll
+        for (int jj = 0; jj < BN; ++jj) s[jj] = Pack2<T>::add(s[jj], ring_row[lc[-jj]]);
+        ptx::mbar_arrive(&bars->ring_release[sb]);
+      }
+      if (has_p2c) {
+        ok = ptx::mbar_wait(&bars->pt_ready, (uint32_t)t & 1u, abort_flag, status_word, 21);
+        if (!ok) break;
+        const uint16_t* lp = lutP + e0;
+        const uint16_t* pt_rel = pt16 - (int)win_lo[t] * PT_PITCH_H;  // PT row of slot s is pt_rel + PT_PITCH_H*s
+#pragma unroll
+        for (int jj = 0; jj < BN; ++jj) s[jj] = Pack2<T>::add(s[jj], pt_rel[lp[-jj] + jj]);
+        ptx::mbar_arrive(&bars->pt_release);
+      }
+
+      ok = attn::softmax_tile_tail<T, D>(s, st, kbits[2 * t], kbits[2 * t + 1], L - j0, q_keep, cscale, t, t_o,
+                                         tmem_base + lane_base + COL_P + sb * (BN / 2), &bars->o_ready,
+                                         &bars->p_full[sb], abort_flag, status_word);
+    }
+    T* out = reinterpret_cast<T*>(p.out) + ((long long)b * L + (row_ok ? i : 0)) * ((long long)H * D) + (long long)h * D;
+    attn::softmax_store_row<T, D>(st, ok, row_ok, n_kt, t_o, out, &bars->o_ready, abort_flag, status_word);
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 9) ptx::tmem_dealloc(tmem_base, kTmemCols);
+}
+
+template <typename T, int D>
+int launch_fused_typed(const DflAttnTablesParams& p, cudaStream_t stream) {
+  using LO = FLayout<D>;
+  const int L = p.seq_len, BH = p.batch * p.heads, A = p.n_active;
+  const uint64_t row = (uint64_t)D * sizeof(T), seq = (uint64_t)L * row, table = (uint64_t)A * row;
+  CUtensorMap tq, tk, tv, tpk, tpq;
+  int rc = encode_tensor_map_3d(&tq, p.q, D, L, BH, row, seq, D, BM, LO::kRowBytes);
+  if (rc == DFL_OK) rc = encode_tensor_map_3d(&tk, p.k, D, L, BH, row, seq, D, BN, LO::kRowBytes);
+  if (rc == DFL_OK) rc = encode_tensor_map_3d(&tv, p.v, D, L, BH, row, seq, D, BN, LO::kRowBytes);
+  // a disabled term reuses the other table's map; it is never dereferenced
+  const void* pk = p.pos_key ? p.pos_key : p.pos_query;
+  const void* pq = p.pos_query ? p.pos_query : p.pos_key;
+  if (rc == DFL_OK) rc = encode_tensor_map_3d(&tpk, pk, D, A, p.heads, row, table, D, BN, LO::kRowBytes);
+  if (rc == DFL_OK) rc = encode_tensor_map_3d(&tpq, pq, D, A, p.heads, row, table, D, BM, LO::kRowBytes);
+  if (rc != DFL_OK) return rc;
+
+  constexpr int kMaxSmem = 232448;
+  const int smem = LO::total(L);
+  if (smem > kMaxSmem) return fail(DFL_ERR_TOO_LARGE, "seq_len %d needs %d bytes of shared memory", L, smem);
+  // 512 TMEM columns per CTA: exactly one CTA may be resident per SM
+  const int smem_request = smem < kMaxSmem / 2 + 1024 ? kMaxSmem / 2 + 1024 : smem;
+
+  auto kernel = attention_fused_kernel<T, D>;
+  static int configured_smem = 0;
+  if (smem_request > configured_smem) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_request);
+    if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "attention_fused smem opt-in: %s", cudaGetErrorString(e));
+    configured_smem = smem_request;
+  }
+  int* status_word = p.status;
+  if (!status_word) {
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status_word), g_attn_fused_status);
+    if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "status word: %s", cudaGetErrorString(e));
+  }
+  dim3 grid((L + BM - 1) / BM, BH);
+  if (grid.y > 65535) return fail(DFL_ERR_TOO_LARGE, "batch*heads > 65535");
+  kernel<<<grid, kThreads, smem_request, stream>>>(tq, tk, tv, tpk, tpq, p, status_word);
+  return check_launch("attention_fused_kernel");
+}
+
+}  // namespace
+
+bool attention_fused_supported(const DflAttnTablesParams& p) {
+  return p.dtype != DFL_F32 && (p.head_dim == 32 || p.head_dim == 64) && (p.pos_key || p.pos_query) &&
+         p.n_active >= 1 && p.n_active <= 992 && p.seq_len <= 2048;
+}
+
+int launch_attention_fused(const DflAttnTablesParams& p, cudaStream_t stream) {
+  if (!attention_fused_supported(p)) return fail(DFL_ERR_UNSUPPORTED, "configuration not covered by the fused-score kernel");
+  if (p.dtype == DFL_F16)
+    return p.head_dim == 64 ? launch_fused_typed<__half, 64>(p, stream) : launch_fused_typed<__half, 32>(p, stream);
+  return p.head_dim == 64 ? launch_fused_typed<__nv_bfloat16, 64>(p, stream)
+                          : launch_fused_typed<__nv_bfloat16, 32>(p, stream);
+}
+
+}  // namespace dfl

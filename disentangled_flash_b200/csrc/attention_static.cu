@@ -50,7 +50,7 @@ extern "C" {
 
 size_t dfl_static_scratch_bytes(void) { return kStaticScratchBytes; }
 
-int dfl_attention_fwd_static(const DflAttnStaticParams* p, void* stream) {
+int dfl_attention_fwd_static(const DflAttnTablesParams* p, void* stream) {
   if (!p) return fail(DFL_ERR_BAD_ARG, "null params");
   if (p->batch < 1 || p->heads < 1 || p->seq_len < 1) return fail(DFL_ERR_BAD_ARG, "non-positive size");
   const bool has_c2p = p->pos_key != nullptr, has_p2c = p->pos_query != nullptr;

@@ -26,8 +26,7 @@
 //              16-byte cp.async that signal an mbarrier on completion.
 // The slot table lut (delta -> local slot) is monotone with steps of 0 or 1, so
 // everything a tile needs from a c2p/p2c row is one contiguous window.
-#include "dfl_common.cuh"
-#include "tcgen05_ptx.cuh"
+#include "attention_tc_common.cuh"
 
 namespace dfl {
 
@@ -35,8 +34,9 @@ __device__ int g_attn_status = 0;
 
 namespace {
 
-constexpr int BM = 128;          // query rows per CTA
-constexpr int BN = 64;           // keys per tile
+using attn::BM;  // 128 query rows per CTA
+using attn::BN;  // 64 keys per tile
+using attn::Pack2;
 constexpr int kThreads = 256;
 constexpr int KV_STAGES = 2;
 constexpr int C_CHUNKS = 9;      // 16-byte chunks per staged c2p row: (BN-1+7)/8 + 1
@@ -86,23 +86,6 @@ struct Barriers {
 };
 static_assert(sizeof(Barriers) <= 256, "barrier block too large");
 
-template <typename T>
-struct Pack2;
-template <>
-struct Pack2<__half> {
-  static __device__ __forceinline__ uint32_t pack(float a, float b) {
-    __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-  }
-};
-template <>
-struct Pack2<__nv_bfloat16> {
-  static __device__ __forceinline__ uint32_t pack(float a, float b) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-  }
-};
-
 struct RoleCtx {
   unsigned char* smem;
   Barriers* bars;
@@ -113,13 +96,6 @@ struct RoleCtx {
   int L, H, b, h, i0, n_kt;
   bool has_c2p, has_p2c;
 };
-
-__device__ __forceinline__ float ld_smem_elem(const unsigned char* base, uint32_t byte_off, __half) {
-  return __half2float(*reinterpret_cast<const __half*>(base + byte_off));
-}
-__device__ __forceinline__ float ld_smem_elem(const unsigned char* base, uint32_t byte_off, __nv_bfloat16) {
-  return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(base + byte_off));
-}
 
 // Softmax role: executed by warps 0-3, thread (warp*32+lane) owns query row i0 + warp*32 + lane,
 // which is TMEM lane warp*32+lane of every accumulator.
@@ -139,8 +115,7 @@ __device__ __forceinline__ void softmax_role(const RoleCtx& c, const DflAttnPara
   const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
   const uint32_t t_o = c.tmem_base + lane_base + COL_O;
 
-  float m_run = -INFINITY;  // running row maximum, in unscaled score units
-  float l_run = 0.0f;
+  attn::RowState st;
   bool ok = true;
 
   for (int kt = 0; kt < c.n_kt && ok; ++kt) {
@@ -150,16 +125,7 @@ __device__ __forceinline__ void softmax_role(const RoleCtx& c, const DflAttnPara
     if (!ok) break;
     ptx::tc_fence_after();
     float s[BN];
-    {
-      uint32_t raw[32];
-#pragma unroll
-      for (int half = 0; half < BN / 32; ++half) {
-        ptx::tmem_ld32(c.tmem_base + lane_base + COL_S + sb * BN + half * 32, raw);
-        ptx::tmem_wait_ld();
-#pragma unroll
-        for (int x = 0; x < 32; ++x) s[half * 32 + x] = __uint_as_float(raw[x]);
-      }
-    }
+    attn::load_scores(c.tmem_base + lane_base + COL_S + sb * BN, s);
     ptx::tc_fence_before();
     ptx::mbar_arrive(&bars->s_free[sb]);  // S buffer may be overwritten by the tile after next
 
@@ -174,103 +140,30 @@ __device__ __forceinline__ void softmax_role(const RoleCtx& c, const DflAttnPara
       const unsigned char* c_row = stage + r * C_PITCH - c_lo;
       const uint32_t p_lo = c.lut_s[LUT_LO_PAD + c.i0 - j0 + (L - 1) - (BN - 1)] & ~15u;
       const unsigned char* p_row = stage + BM * C_PITCH - p_lo;
+      auto elem = [](const unsigned char* base, uint32_t off) { return *reinterpret_cast<const uint16_t*>(base + off); };
       if (c.has_c2p && c.has_p2c) {
 #pragma unroll
         for (int jj = 0; jj < BN; ++jj) {
           const uint32_t off = lut_i[-jj];
-          s[jj] += ld_smem_elem(c_row, off, T()) + ld_smem_elem(p_row + jj * P_PITCH, off, T());
+          s[jj] = Pack2<T>::add(Pack2<T>::add(s[jj], elem(c_row, off)), elem(p_row + jj * P_PITCH, off));
         }
       } else if (c.has_c2p) {
 #pragma unroll
-        for (int jj = 0; jj < BN; ++jj) s[jj] += ld_smem_elem(c_row, lut_i[-jj], T());
+        for (int jj = 0; jj < BN; ++jj) s[jj] = Pack2<T>::add(s[jj], elem(c_row, lut_i[-jj]));
       } else {
 #pragma unroll
-        for (int jj = 0; jj < BN; ++jj) s[jj] += ld_smem_elem(p_row + jj * P_PITCH, lut_i[-jj], T());
+        for (int jj = 0; jj < BN; ++jj) s[jj] = Pack2<T>::add(s[jj], elem(p_row + jj * P_PITCH, lut_i[-jj]));
       }
       ptx::mbar_arrive(&bars->bias_empty[bs]);
     }
 
-    // mask: keys >= L and padded keys -> -inf; a padded query row -> 0 on every in-range key
-    const uint32_t kb0 = c.kbits[2 * kt], kb1 = c.kbits[2 * kt + 1];
-    const int n_in = L - j0;  // in-range keys of this tile (>= 1)
-    if (!q_keep) {
-#pragma unroll
-      for (int jj = 0; jj < BN; ++jj) s[jj] = jj < n_in ? 0.0f : -INFINITY;
-    } else if ((kb0 & kb1) != 0xffffffffu) {
-#pragma unroll
-      for (int jj = 0; jj < BN; ++jj) {
-        const uint32_t w = jj < 32 ? kb0 : kb1;
-        if (!((w >> (jj & 31)) & 1u)) s[jj] = -INFINITY;
-      }
-    }
-
-    float tile_max = -INFINITY;
-#pragma unroll
-    for (int jj = 0; jj < BN; ++jj) tile_max = fmaxf(tile_max, s[jj]);
-    const float m_new = fmaxf(m_run, tile_max);
-    const float m_use = m_new == -INFINITY ? 0.0f : m_new;  // nothing attended yet: avoid inf - inf
-    const float corr = ptx::ex2_approx((m_run - m_use) * cscale);  // 0 when m_run = -inf
-    const float neg_m = -m_use * cscale;
-    float tile_sum = 0.0f;
-    uint32_t packed[BN / 2];
-#pragma unroll
-    for (int jj = 0; jj < BN; jj += 2) {
-      const float p0 = ptx::ex2_approx(fmaf(s[jj], cscale, neg_m));
-      const float p1 = ptx::ex2_approx(fmaf(s[jj + 1], cscale, neg_m));
-      tile_sum += p0 + p1;
-      packed[jj / 2] = Pack2<T>::pack(p0, p1);
-    }
-    l_run = l_run * corr + tile_sum;
-    m_run = m_new;
-
-    // O accumulated so far (tiles < kt) must be complete before it is rescaled or P(kt) is consumed
-    if (kt > 0) {
-      ok = ptx::mbar_wait(&bars->o_ready, (uint32_t)(kt - 1) & 1u, abort_flag, c.status_word, 9);
-      if (!ok) break;
-      ptx::tc_fence_after();
-      if (__any_sync(0xffffffffu, corr != 1.0f)) {
-#pragma unroll
-        for (int c0 = 0; c0 < D; c0 += 32) {
-          uint32_t o[32];
-          ptx::tmem_ld32(t_o + c0, o);
-          ptx::tmem_wait_ld();
-#pragma unroll
-          for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * corr);
-          ptx::tmem_st32(t_o + c0, o);
-        }
-      }
-    }
-    {
-      uint32_t (&pk)[32] = *reinterpret_cast<uint32_t (*)[32]>(&packed[0]);
-      ptx::tmem_st32(c.tmem_base + lane_base + COL_P + sb * (BN / 2), pk);
-    }
-    ptx::tmem_wait_st();
-    ptx::tc_fence_before();
-    ptx::mbar_arrive(&bars->p_full[sb]);
+    ok = attn::softmax_tile_tail<T, D>(s, st, c.kbits[2 * kt], c.kbits[2 * kt + 1], L - j0, q_keep, cscale, kt, t_o,
+                                       c.tmem_base + lane_base + COL_P + sb * (BN / 2), &bars->o_ready,
+                                       &bars->p_full[sb], abort_flag, c.status_word);
   }
 
-  // epilogue: wait for the last PV, normalise, store out[b, i, h*D : (h+1)*D]
-  if (ok) ok = ptx::mbar_wait(&bars->o_ready, (uint32_t)(c.n_kt - 1) & 1u, abort_flag, c.status_word, 10);
-  ptx::tc_fence_after();
-  const float inv = 1.0f / l_run;
   T* out = reinterpret_cast<T*>(p.out) + ((long long)c.b * L + (row_ok ? i : 0)) * ((long long)c.H * D) + (long long)c.h * D;
-#pragma unroll
-  for (int c0 = 0; c0 < D; c0 += 32) {
-    uint32_t o[32];
-    ptx::tmem_ld32(t_o + c0, o);
-    ptx::tmem_wait_ld();
-    if (ok && row_ok) {
-#pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        uint4 pk;
-        pk.x = Pack2<T>::pack(__uint_as_float(o[v * 8 + 0]) * inv, __uint_as_float(o[v * 8 + 1]) * inv);
-        pk.y = Pack2<T>::pack(__uint_as_float(o[v * 8 + 2]) * inv, __uint_as_float(o[v * 8 + 3]) * inv);
-        pk.z = Pack2<T>::pack(__uint_as_float(o[v * 8 + 4]) * inv, __uint_as_float(o[v * 8 + 5]) * inv);
-        pk.w = Pack2<T>::pack(__uint_as_float(o[v * 8 + 6]) * inv, __uint_as_float(o[v * 8 + 7]) * inv);
-        *reinterpret_cast<uint4*>(out + c0 + v * 8) = pk;
-      }
-    }
-  }
+  attn::softmax_store_row<T, D>(st, ok, row_ok, c.n_kt, t_o, out, &bars->o_ready, abort_flag, c.status_word);
 }
 
 template <typename T, int D>

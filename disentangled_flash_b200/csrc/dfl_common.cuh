@@ -98,5 +98,7 @@ int launch_gemm_tc(const GemmDesc& g, cudaStream_t stream);
 
 int launch_attention_simt(const DflAttnParams& p, cudaStream_t stream);
 int launch_attention_tc(const DflAttnParams& p, cudaStream_t stream);
+bool attention_fused_supported(const DflAttnTablesParams& p);
+int launch_attention_fused(const DflAttnTablesParams& p, cudaStream_t stream);
 
 }  // namespace dfl

@@ -177,7 +177,7 @@ DFL_API int dfl_attention_fwd(const DflAttnParams* p, void* stream);
  * kernels overlap on the GPU (different streams, or different host threads) race on it.
  */
 #define DFL_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
-typedef struct DflAttnStaticParams {
+typedef struct DflAttnTablesParams {
   const void* q;          /* [B,H,L,d] */
   const void* k;          /* [B,H,L,d] */
   const void* v;          /* [B,H,L,d] */
@@ -192,9 +192,22 @@ typedef struct DflAttnStaticParams {
   int32_t mask_elem_size; /* 1, 4 or 8 */
   float   scale;
   int32_t dtype, algo;
-} DflAttnStaticParams;
-DFL_API int    dfl_attention_fwd_static(const DflAttnStaticParams* p, void* stream);
+} DflAttnTablesParams;
+DFL_API int    dfl_attention_fwd_static(const DflAttnTablesParams* p, void* stream);
 DFL_API size_t dfl_static_scratch_bytes(void);
+
+/*
+ * Fused attention that takes the pruned position tables instead of precomputed score tensors
+ * (DflAttnTablesParams above): the C2P/P2C scores are produced inside the kernel by tcgen05 from
+ * pos_key / pos_query [H,A,d], rounded to the input type like the separate score GEMMs do, and
+ * consumed from shared memory, so the two [B,H,L,A] tensors are never written to or read from
+ * global memory.  Replaces, in one launch, the two torch.matmul calls (kernel.py:574-585) and the
+ * Triton kernel (kernel.py:137-429).  Covered: FP16/BF16, head_dim 32 or 64, at least one position
+ * term, n_active <= 992, seq_len <= 2048; dfl_attention_tables_supported() tells, and other
+ * configurations return DFL_ERR_UNSUPPORTED (use dfl_pos_scores + dfl_attention_fwd for them).
+ */
+DFL_API int dfl_attention_tables_supported(const DflAttnTablesParams* p);
+DFL_API int dfl_attention_tables_fwd(const DflAttnTablesParams* p, void* stream);
 
 #ifdef __cplusplus
 }
