@@ -16,17 +16,20 @@
 //   P2C: p2c[j, s] = k_j . posQ[s] is needed for the 64 keys of the tile and the window's slots:
 //        computed transposed, PT[s - lo, j] = posQ[lo + ...] . k_j (one or two 128x64x d MMAs),
 //        so that TMEM lanes are slots and all 128 lanes convert.
-// Ten warps:
-//   warps 0-3  softmax (one thread per query row): S from TMEM, gather c2p from the ring row of the
-//              thread and p2c from PT, then the common softmax tail.
-//   warps 4-7  converters: TMEM -> 16-bit -> shared memory for the C2P blocks and the PT tiles.
-//   warp 8     TMA producer: Q, K/V ring, posK blocks, posQ windows.
-//   warp 9     MMA issuer and TMEM owner: C2P blocks, PT, S = Q K^T, O += P V.
+// Twenty-two warps:
+//   warps 0-15  softmax, four threads per query row (warps w, w+4, w+8, w+12 share TMEM lanes 32*(w&3)...):
+//               each owns 16 of the 64 keys of a tile and a quarter of the output columns; S from TMEM,
+//               gather c2p from the ring row and p2c from PT, agree on the row maximum, then the common tail.
+//               Many narrow threads rather than few wide ones: the work is latency bound.
+//   warps 16-19 converters: TMEM -> 16-bit -> shared memory for the C2P blocks and the PT tiles.
+//   warp 20     TMA producer: Q, K/V ring, posK blocks, posQ windows.
+//   warp 21     MMA issuer and TMEM owner: C2P blocks, PT, S = Q K^T, O += P V.
 #include "attention_tc_common.cuh"
 
 namespace dfl {
 
 __device__ int g_attn_fused_status = 0;
+
 
 namespace {
 
@@ -34,11 +37,17 @@ using attn::BM;
 using attn::BN;
 using attn::Pack2;
 
-constexpr int kThreads = 320;
+constexpr int kParts = 4;                       // softmax threads per query row
+constexpr int kSoftmaxWarps = 4 * kParts;
+constexpr int kConvWarp0 = kSoftmaxWarps;       // 4 converter warps
+constexpr int kTmaWarp = kSoftmaxWarps + 4;
+constexpr int kMmaWarp = kSoftmaxWarps + 5;
+constexpr int kThreads = (kSoftmaxWarps + 6) * 32;
 constexpr int KV_STAGES = 2;
 constexpr int RING_BLOCKS = 5;
-constexpr int RING_PITCH_H = RING_BLOCKS * 64 + 2;   // halfs per ring row: 644 bytes = 161 words (odd: conflict free)
-constexpr int PT_ROWS = 256;
+constexpr int RING_SPAN = RING_BLOCKS * 64;          // 320 ring positions; positions 320..383 mirror 0..63
+constexpr int RING_PITCH_H = RING_SPAN + 64 + 2;     // halfs per ring row: 772 bytes = 193 words (odd: conflict free)
+constexpr int PT_ROWS = 192;                         // a tile's window has at most 191 slots
 constexpr int PT_PITCH_H = BN + 2;                    // halfs per PT row: 132 bytes = 33 words
 constexpr int LUT_LO_PAD = BN;
 constexpr int LUT_HI_PAD = BM;
@@ -59,18 +68,22 @@ struct FLayout {
   static constexpr int kK = BN * kRowBytes;            // K tile, V tile, posK block
   static constexpr int offQ = 0;
   static constexpr int offKV = offQ + kQ;                      // KV_STAGES x (K, V)
-  static constexpr int offPQ = offKV + KV_STAGES * 2 * kK;     // posQ window operand: 2 sub-windows of 128 slots
-  static constexpr int offPK = offPQ + 2 * kQ;                 // posK block operand
+  // posQ window operand: slots lo..lo+127 (kQ bytes) then lo+128..lo+191 (kQ/2 bytes).  The second MMA reads
+  // 128 rows from the second part, i.e. runs on into the posK operand that follows; those rows only feed
+  // TMEM lanes 64..127, which nobody reads.
+  static constexpr int offPQ = offKV + KV_STAGES * 2 * kK;
+  static constexpr int offPK = offPQ + kQ + kQ / 2;            // posK block operand (kK = kQ/2 bytes)
   static constexpr int offRing = offPK + kK;                   // C2P ring [128][RING_PITCH_H]
   static constexpr int offPT = offRing + BM * RING_PITCH_H * 2;  // PT staging [256][PT_PITCH_H]
   static constexpr int offBar = (offPT + PT_ROWS * PT_PITCH_H * 2 + 15) & ~15;
   static constexpr int kBarBytes = 512;
-  static constexpr int offTables = offBar + kBarBytes;
-  // tables: lutC u16[n_lut], lutP u16[n_lut], win_lo/win_hi int16[n_kt] each, kbits u32[2*n_kt]
+  static constexpr int offXchg = offBar + kBarBytes;            // row exchange: [2][kParts][BM] floats
+  static constexpr int offTables = offXchg + 2 * kParts * BM * 4;
+  // tables: stepM u32[n_lut], lutS u16[n_lut], win_lo/win_hi int16[n_kt] each, kbits u32[2*n_kt]
   static int total(int L) {
     const int n_lut = 2 * L - 1 + LUT_LO_PAD + LUT_HI_PAD;
     const int n_kt = (L + BN - 1) / BN;
-    return offTables + ((4 * n_lut + 15) & ~15) + ((4 * n_kt + 15) & ~15) + 8 * n_kt + 1024;
+    return offTables + ((6 * n_lut + 15) & ~15) + ((4 * n_kt + 15) & ~15) + 8 * n_kt + 1024;
   }
 };
 
@@ -86,14 +99,15 @@ struct FBarriers {
   uint64_t c2p_ready[2];             // ring holds everything tile t needs
   uint64_t ring_release[2];          // softmax threads finished gathering C2P of tile t
   uint64_t pt_ready, pt_release;     // PT staging in shared memory
+  uint64_t pair[4];                  // per lane quarter: the two softmax warps of a row exchange maxima
   uint32_t tmem_base;
   int abort_flag;
 };
 static_assert(sizeof(FBarriers) <= 512, "barrier block too large");
 
 struct FTables {
-  const uint16_t* lutC;   // ring element index of the slot of each delta
-  const uint16_t* lutP;   // PT_PITCH_H * slot
+  const uint32_t* stepM;  // bit x of entry e: slot(e - x) - slot(e - x - 1), x = 0..30 (slot steps are 0 or 1)
+  const uint16_t* lutS;   // slot of each (padded) delta index
   const int16_t* win_lo;  // per key tile: lowest slot touched
   const int16_t* win_hi;  // per key tile: highest slot touched
   const uint32_t* kbits;  // key keep-bits
@@ -114,7 +128,8 @@ template <typename T, int D>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_pk,
-                       const __grid_constant__ CUtensorMap tmap_pq, const DflAttnTablesParams p, int* status_word) {
+                       const __grid_constant__ CUtensorMap tmap_pq, const __grid_constant__ CUtensorMap tmap_pq64,
+                       const DflAttnTablesParams p, int* status_word) {
   using LO = FLayout<D>;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
@@ -128,13 +143,14 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   const int n_kt = (L + BN - 1) / BN;
   const bool has_c2p = p.pos_key != nullptr, has_p2c = p.pos_query != nullptr;
   const int n_lut = 2 * L - 1 + LUT_LO_PAD + LUT_HI_PAD;
+  TRACE_DECL
 
-  uint16_t* lutC = reinterpret_cast<uint16_t*>(smem + LO::offTables);
-  uint16_t* lutP = lutC + n_lut;
-  int16_t* win_lo = reinterpret_cast<int16_t*>(smem + LO::offTables + ((4 * n_lut + 15) & ~15));
+  uint32_t* stepM = reinterpret_cast<uint32_t*>(smem + LO::offTables);
+  uint16_t* lutS = reinterpret_cast<uint16_t*>(stepM + n_lut);
+  int16_t* win_lo = reinterpret_cast<int16_t*>(smem + LO::offTables + ((6 * n_lut + 15) & ~15));
   int16_t* win_hi = win_lo + n_kt;
-  uint32_t* kbits = reinterpret_cast<uint32_t*>(smem + LO::offTables + ((4 * n_lut + 15) & ~15) + ((4 * n_kt + 15) & ~15));
-  const FTables tb{lutC, lutP, win_lo, win_hi, kbits};
+  uint32_t* kbits = reinterpret_cast<uint32_t*>(smem + LO::offTables + ((6 * n_lut + 15) & ~15) + ((4 * n_kt + 15) & ~15));
+  const FTables tb{stepM, lutS, win_lo, win_hi, kbits};
 
   // ------------------------------------------------------------------ setup
   if (threadIdx.x == 0) {
@@ -145,10 +161,11 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     }
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(&bars->s_full[s], 1);
-      ptx::mbar_init(&bars->s_free[s], 128);
-      ptx::mbar_init(&bars->p_full[s], 128);
-      ptx::mbar_init(&bars->c2p_ready[s], 128);
-      ptx::mbar_init(&bars->ring_release[s], 128);
+      // one elected lane per warp arrives (after __syncwarp): kSoftmaxWarps softmax warps, 4 converter warps
+      ptx::mbar_init(&bars->s_free[s], kSoftmaxWarps);
+      ptx::mbar_init(&bars->p_full[s], kSoftmaxWarps);
+      ptx::mbar_init(&bars->c2p_ready[s], 4);
+      ptx::mbar_init(&bars->ring_release[s], kSoftmaxWarps);
     }
     ptx::mbar_init(&bars->o_ready, 1);
     ptx::mbar_init(&bars->pk_full, 1);
@@ -156,32 +173,45 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     ptx::mbar_init(&bars->pq_full, 1);
     ptx::mbar_init(&bars->pq_empty, 1);
     ptx::mbar_init(&bars->cnew_full, 1);
-    ptx::mbar_init(&bars->cnew_free, 128);
+    ptx::mbar_init(&bars->cnew_free, 4);
     ptx::mbar_init(&bars->pt_full, 1);
-    ptx::mbar_init(&bars->pt_free, 128);
-    ptx::mbar_init(&bars->pt_ready, 128);
-    ptx::mbar_init(&bars->pt_release, 128);
+    ptx::mbar_init(&bars->pt_free, 4);
+    ptx::mbar_init(&bars->pt_ready, 4);
+    ptx::mbar_init(&bars->pt_release, kSoftmaxWarps);
+    for (int q = 0; q < 4; ++q) ptx::mbar_init(&bars->pair[q], kParts);
     bars->abort_flag = 0;
     ptx::fence_mbar_init();
   }
-  if (warp == 8 && lane == 0) {
+  if (warp == kTmaWarp && lane == 0) {
     ptx::prefetch_tensormap(&tmap_q);
     ptx::prefetch_tensormap(&tmap_k);
     ptx::prefetch_tensormap(&tmap_v);
     ptx::prefetch_tensormap(&tmap_pk);
     ptx::prefetch_tensormap(&tmap_pq);
+    ptx::prefetch_tensormap(&tmap_pq64);
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     ptx::tmem_alloc(&bars->tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
   // slot tables, edge-replicated so that out-of-range (i, j) pairs resolve inside the tile's window
-  for (int e = threadIdx.x; e < n_lut; e += kThreads) {
-    int src = e - LUT_LO_PAD;
-    src = src < 0 ? 0 : (src > 2 * L - 2 ? 2 * L - 2 : src);
-    const int s = p.lut[src];
-    lutC[e] = (uint16_t)(((s >> 6) % RING_BLOCKS) * 64 + (s & 63));
-    lutP[e] = (uint16_t)(PT_PITCH_H * s);
+  {
+    auto slot_at = [&](int e) {
+      int src = e - LUT_LO_PAD;
+      src = src < 0 ? 0 : (src > 2 * L - 2 ? 2 * L - 2 : src);
+      return (int)p.lut[src];
+    };
+    for (int e = threadIdx.x; e < n_lut; e += kThreads) {
+      uint32_t m = 0;
+      int cur = slot_at(e);
+      lutS[e] = (uint16_t)cur;
+      for (int x = 0; x < 31 && e - x - 1 >= 0; ++x) {
+        const int nxt = slot_at(e - x - 1);
+        m |= (uint32_t)(cur - nxt) << x;
+        cur = nxt;
+      }
+      stepM[e] = m;
+    }
   }
   for (int t = threadIdx.x; t < n_kt; t += kThreads) {
     int a = i0 - (t * BN + BN - 1) + (L - 1), z = i0 + (BM - 1) - t * BN + (L - 1);
@@ -201,7 +231,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   ptx::tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
-  if (warp == 8) {
+  if (warp == kTmaWarp) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       bool ok = true;
@@ -222,22 +252,24 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         if (has_p2c) {
           ok = ptx::mbar_wait(&bars->pq_empty, ((uint32_t)t & 1u) ^ 1u, abort_flag, status_word, 12);
           if (!ok) break;
+          TRACE(32);
           const int lo = win_lo[t];
           const bool two = win_hi[t] - lo >= 128;
-          ptx::mbar_arrive_expect_tx(&bars->pq_full, (uint32_t)(two ? 2 * LO::kQ : LO::kQ));
+          ptx::mbar_arrive_expect_tx(&bars->pq_full, (uint32_t)(two ? LO::kQ + LO::kQ / 2 : LO::kQ));
           ptx::tma_load_3d(smem + LO::offPQ, &tmap_pq, &bars->pq_full, 0, lo, h);
-          if (two) ptx::tma_load_3d(smem + LO::offPQ + LO::kQ, &tmap_pq, &bars->pq_full, 0, lo + 128, h);
+          if (two) ptx::tma_load_3d(smem + LO::offPQ + LO::kQ, &tmap_pq64, &bars->pq_full, 0, lo + 128, h);
         }
         const int s = t % KV_STAGES;
         ok = ptx::mbar_wait(&bars->kv_empty[s], ((uint32_t)(t / KV_STAGES) & 1u) ^ 1u, abort_flag, status_word, 1);
         if (!ok) break;
+        TRACE(33);
         ptx::mbar_arrive_expect_tx(&bars->kv_full[s], (uint32_t)(2 * LO::kK));
         unsigned char* kv = smem + LO::offKV + s * 2 * LO::kK;
         ptx::tma_load_3d(kv, &tmap_k, &bars->kv_full[s], 0, t * BN, bh);
         ptx::tma_load_3d(kv + LO::kK, &tmap_v, &bars->kv_full[s], 0, t * BN, bh);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarp) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr int is_bf16 = __is_same(T, __nv_bfloat16) ? 1 : 0;
@@ -269,6 +301,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           for (int x = 0; x < jobs.count; ++x, ++n_job) {
             if (!ptx::mbar_wait(&bars->pk_full, n_job & 1u, abort_flag, status_word, 13)) return false;
             if (!ptx::mbar_wait(&bars->cnew_free, (n_job & 1u) ^ 1u, abort_flag, status_word, 14)) return false;
+            TRACE(22);
             ptx::tc_fence_after();
             mma_128x64(COL_CNEW, q_addr, pk_addr);
             ptx::umma_commit(&bars->pk_empty);
@@ -277,10 +310,12 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         }
         const int s = t % KV_STAGES, sb = t & 1;
         if (!ptx::mbar_wait(&bars->kv_full[s], (uint32_t)(t / KV_STAGES) & 1u, abort_flag, status_word, 3)) return false;
+        TRACE(23);
         const uint32_t k_addr = ptx::smem_u32(smem + LO::offKV + s * 2 * LO::kK);
         if (has_p2c) {
           if (!ptx::mbar_wait(&bars->pq_full, (uint32_t)t & 1u, abort_flag, status_word, 15)) return false;
           if (!ptx::mbar_wait(&bars->pt_free, ((uint32_t)t & 1u) ^ 1u, abort_flag, status_word, 16)) return false;
+          TRACE(25);
           ptx::tc_fence_after();
           mma_128x64(COL_PT, pq_addr, k_addr);
           if (win_hi[t] - win_lo[t] >= 128) mma_128x64(COL_PT + BN, pq_addr + LO::kQ, k_addr);
@@ -288,6 +323,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           ptx::umma_commit(&bars->pt_full);
         }
         if (!ptx::mbar_wait(&bars->s_free[sb], ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag, status_word, 4)) return false;
+        TRACE(26);
         ptx::tc_fence_after();
         mma_128x64(COL_S + sb * BN, q_addr, k_addr);
         ptx::umma_commit(&bars->s_full[sb]);
@@ -301,6 +337,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         const int s = t % KV_STAGES, sb = t & 1;
         ok = ptx::mbar_wait(&bars->p_full[sb], (uint32_t)(t >> 1) & 1u, abort_flag, status_word, 5);
         if (!ok) break;
+        TRACE(27);
         ptx::tc_fence_after();
         const uint32_t v_addr = ptx::smem_u32(smem + LO::offKV + s * 2 * LO::kK + LO::kK);
 #pragma unroll
@@ -311,9 +348,10 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         }
         ptx::umma_commit(&bars->kv_empty[s]);
         ptx::umma_commit(&bars->o_ready);
+        TRACE(28);
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp >= kConvWarp0) {
     // -------------------------------------------------------------- converters
     // Thread (quarter q = warp & 3, lane) owns TMEM lane 32q + lane: a query row for C2P blocks,
     // a slot (relative to the window start) for PT tiles.
@@ -325,16 +363,21 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     bool ok = true;
 
     // 64 fp32 columns at t_src -> 64 16-bit values at dst (4-byte aligned), rounded like a GEMM epilogue
-    auto convert_64 = [&](uint32_t t_src, unsigned char* dst) {
+    // (all lanes must execute the TMEM load; `store` and `mirror` only gate the shared-memory writes)
+    auto convert_64 = [&](uint32_t t_src, unsigned char* dst, int mirror = 0, bool store = true) {
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t raw[32];
         ptx::tmem_ld32(t_src + half * 32, raw);
         ptx::tmem_wait_ld();
+        if (store) {
 #pragma unroll
-        for (int x = 0; x < 32; x += 2)
-          *reinterpret_cast<uint32_t*>(dst + half * 64 + x * 2) =
-              Pack2<T>::pack(__uint_as_float(raw[x]), __uint_as_float(raw[x + 1]));
+          for (int x = 0; x < 32; x += 2) {
+            const uint32_t w = Pack2<T>::pack(__uint_as_float(raw[x]), __uint_as_float(raw[x + 1]));
+            *reinterpret_cast<uint32_t*>(dst + half * 64 + x * 2) = w;
+            if (mirror) *reinterpret_cast<uint32_t*>(dst + mirror + half * 64 + x * 2) = w;
+          }
+        }
       }
     };
 
@@ -346,87 +389,143 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         // two-phase c2p_ready barriers rely on.
         ok = ptx::mbar_wait(&bars->ring_release[t & 1], ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag, status_word, 17);
         if (!ok) break;
+        TRACE(11);
         for (int x = 0; x < jobs.count && ok; ++x, ++n_job) {
           ok = ptx::mbar_wait(&bars->cnew_full, n_job & 1u, abort_flag, status_word, 18);
           if (!ok) break;
+          TRACE(12);
           ptx::tc_fence_after();
           const int blk = jobs.first - x;
-          convert_64(tmem_base + lane_base + COL_CNEW, ring_row + (blk % RING_BLOCKS) * 128);
+          // the block at ring position 0 is mirrored at position 5 so that a row's run never wraps
+          convert_64(tmem_base + lane_base + COL_CNEW, ring_row + (blk % RING_BLOCKS) * 128,
+                     blk % RING_BLOCKS == 0 ? RING_SPAN * 2 : 0);
           ptx::tc_fence_before();
-          ptx::mbar_arrive(&bars->cnew_free);
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&bars->cnew_free);
+          TRACE(13);
         }
         if (!ok) break;
-        ptx::mbar_arrive(&bars->c2p_ready[t & 1]);
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&bars->c2p_ready[t & 1]);
       }
       if (has_p2c) {
         ok = ptx::mbar_wait(&bars->pt_full, (uint32_t)t & 1u, abort_flag, status_word, 19);
         if (!ok) break;
+        TRACE(14);
         ptx::tc_fence_after();
         // the staging tile is single-buffered: tile t-1 must have been gathered
         ok = ptx::mbar_wait(&bars->pt_release, ((uint32_t)t & 1u) ^ 1u, abort_flag, status_word, 20);
         if (!ok) break;
+        TRACE(15);
         convert_64(tmem_base + lane_base + COL_PT, pt_base + row * (PT_PITCH_H * 2));
-        if (win_hi[t] - win_lo[t] >= 128)
-          convert_64(tmem_base + lane_base + COL_PT + BN, pt_base + (128 + row) * (PT_PITCH_H * 2));
+        if (win_hi[t] - win_lo[t] >= 128)  // slots lo+128 .. lo+191 sit in lanes 0..63 of the second accumulator
+          convert_64(tmem_base + lane_base + COL_PT + BN, pt_base + (128 + (row & 63)) * (PT_PITCH_H * 2), 0, row < 64);
         ptx::tc_fence_before();
-        ptx::mbar_arrive(&bars->pt_free);
-        ptx::mbar_arrive(&bars->pt_ready);
+        __syncwarp();
+        if (lane == 0) {
+          ptx::mbar_arrive(&bars->pt_free);
+          ptx::mbar_arrive(&bars->pt_ready);
+        }
+        TRACE(16);
       }
     }
   } else {
     // ----------------------------------------------------------------- softmax
-    const int r = warp * 32 + lane;
+    constexpr int W = BN / kParts;                 // keys per thread and tile
+    const int q4 = warp & 3, part = warp >> 2;     // lane quarter, which part of the keys / output columns
+    const int r = q4 * 32 + lane;
     const int i = i0 + r;
     const bool row_ok = i < L;
     const bool q_keep = row_ok && mask_keep(p.mask, p.mask_elem_size, (long long)b * L + i);
     const float cscale = p.scale * 1.4426950408889634f;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    const uint32_t t_o = tmem_base + lane_base + COL_O;
+    const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
+    const uint32_t t_o_part = tmem_base + lane_base + COL_O + part * (D / kParts);
     const uint16_t* ring_row = reinterpret_cast<const uint16_t*>(smem + LO::offRing) + r * RING_PITCH_H;
     const uint16_t* pt16 = reinterpret_cast<const uint16_t*>(smem + LO::offPT);
+    const attn::RowExchange xc{reinterpret_cast<float*>(smem + LO::offXchg), &bars->pair[q4]};
     attn::RowState st;
     bool ok = true;
 
     for (int t = 0; t < n_kt && ok; ++t) {
-      const int sb = t & 1, j0 = t * BN;
+      const int sb = t & 1, j0 = t * BN + part * W;  // first key of this thread's part
       ok = ptx::mbar_wait(&bars->s_full[sb], (uint32_t)(t >> 1) & 1u, abort_flag, status_word, 7);
       if (!ok) break;
+      TRACE(1);
       ptx::tc_fence_after();
-      float s[BN];
-      attn::load_scores(tmem_base + lane_base + COL_S + sb * BN, s);
+      float s[W];
+      {
+        uint32_t raw[W];
+        attn::tmem_ld_n(tmem_base + lane_base + COL_S + sb * BN + part * W, raw);
+        ptx::tmem_wait_ld();
+#pragma unroll
+        for (int x = 0; x < W; ++x) s[x] = __uint_as_float(raw[x]);
+      }
       ptx::tc_fence_before();
-      ptx::mbar_arrive(&bars->s_free[sb]);
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&bars->s_free[sb]);
+      TRACE(2);
 
-      const int e0 = LUT_LO_PAD + i - j0 + (L - 1);  // table index of pair (i, j0); pair (i, j0+jj) is e0 - jj
+      // Slots of this thread's W pairs: s_0 = slot(i, j0) and s_{x+1} = s_x - step bit x (steps are 0 or 1), so the
+      // two gathers walk their row with a running address instead of one table lookup per element.
+      const int e0 = LUT_LO_PAD + i - j0 + (L - 1);  // table index of pair (i, j0); pair (i, j0+x) is e0 - x
+      const uint32_t steps = stepM[e0];
+      const int s0 = lutS[e0];
       if (has_c2p) {
         ok = ptx::mbar_wait(&bars->c2p_ready[sb], (uint32_t)(t >> 1) & 1u, abort_flag, status_word, 8);
         if (!ok) break;
-        const uint16_t* lc = lutC + e0;
-#pragma unroll
-        for (int jj = 0; jj < BN; ++jj) s[jj] = Pack2<T>::add(s[jj], ring_row[lc[-jj]]);
-        ptx::mbar_arrive(&bars->ring_release[sb]);
       }
       if (has_p2c) {
         ok = ptx::mbar_wait(&bars->pt_ready, (uint32_t)t & 1u, abort_flag, status_word, 21);
         if (!ok) break;
-        const uint16_t* lp = lutP + e0;
-        const uint16_t* pt_rel = pt16 - (int)win_lo[t] * PT_PITCH_H;  // PT row of slot s is pt_rel + PT_PITCH_H*s
-#pragma unroll
-        for (int jj = 0; jj < BN; ++jj) s[jj] = Pack2<T>::add(s[jj], pt_rel[lp[-jj] + jj]);
-        ptx::mbar_arrive(&bars->pt_release);
       }
+      TRACE(3);
+      {
+        // C2P: ring position of slot s0; the mirror makes pos-(W-1) .. pos contiguous.
+        int cidx = s0 % RING_SPAN;
+        if (cidx < W - 1) cidx += RING_SPAN;
+        // P2C: PT[slot - lo][key]; the row moves down one pitch whenever the slot steps, the column follows x.
+        int pidx = (s0 - (int)win_lo[t]) * PT_PITCH_H + part * W;
+        uint16_t cval[W], pval[W];
+#pragma unroll
+        for (int x = 0; x < W; ++x) {
+          if (has_c2p) cval[x] = ring_row[cidx];
+          if (has_p2c) pval[x] = pt16[pidx + x];
+          if (steps & (1u << x)) {
+            cidx -= 1;
+            pidx -= PT_PITCH_H;
+          }
+        }
+        if (has_c2p) {
+#pragma unroll
+          for (int x = 0; x < W; ++x) s[x] = Pack2<T>::add(s[x], cval[x]);
+        }
+        if (has_p2c) {
+#pragma unroll
+          for (int x = 0; x < W; ++x) s[x] = Pack2<T>::add(s[x], pval[x]);
+        }
+        __syncwarp();
+        if (lane == 0) {
+          if (has_c2p) ptx::mbar_arrive(&bars->ring_release[sb]);
+          if (has_p2c) ptx::mbar_arrive(&bars->pt_release);
+        }
+      }
+      TRACE(6);
 
-      ok = attn::softmax_tile_tail<T, D>(s, st, kbits[2 * t], kbits[2 * t + 1], L - j0, q_keep, cscale, t, t_o,
-                                         tmem_base + lane_base + COL_P + sb * (BN / 2), &bars->o_ready,
-                                         &bars->p_full[sb], abort_flag, status_word);
+      const uint32_t kb = kbits[(j0 >> 5)] >> (j0 & 31);
+      ok = attn::softmax_part_tail<T, D, kParts>(s, st, kb, L - j0, q_keep, cscale, t, part, r, xc, t_o_part,
+                                                 tmem_base + lane_base + COL_P + sb * (BN / 2) + part * (W / 2),
+                                                 &bars->o_ready, &bars->p_full[sb], abort_flag, status_word TRACE_ARG);
+      TRACE(7);
     }
-    T* out = reinterpret_cast<T*>(p.out) + ((long long)b * L + (row_ok ? i : 0)) * ((long long)H * D) + (long long)h * D;
-    attn::softmax_store_row<T, D>(st, ok, row_ok, n_kt, t_o, out, &bars->o_ready, abort_flag, status_word);
+    T* out = reinterpret_cast<T*>(p.out) + ((long long)b * L + (row_ok ? i : 0)) * ((long long)H * D) +
+             (long long)h * D + part * (D / kParts);
+    attn::softmax_part_store<T, D, kParts>(st, ok, row_ok, n_kt, part, r, xc, t_o_part, out, &bars->o_ready,
+                                           abort_flag, status_word);
   }
 
   ptx::tc_fence_before();
   __syncthreads();
-  if (warp == 9) ptx::tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == kMmaWarp) ptx::tmem_dealloc(tmem_base, kTmemCols);
 }
 
 template <typename T, int D>
@@ -434,7 +533,7 @@ int launch_fused_typed(const DflAttnTablesParams& p, cudaStream_t stream) {
   using LO = FLayout<D>;
   const int L = p.seq_len, BH = p.batch * p.heads, A = p.n_active;
   const uint64_t row = (uint64_t)D * sizeof(T), seq = (uint64_t)L * row, table = (uint64_t)A * row;
-  CUtensorMap tq, tk, tv, tpk, tpq;
+  CUtensorMap tq, tk, tv, tpk, tpq, tpq64;
   int rc = encode_tensor_map_3d(&tq, p.q, D, L, BH, row, seq, D, BM, LO::kRowBytes);
   if (rc == DFL_OK) rc = encode_tensor_map_3d(&tk, p.k, D, L, BH, row, seq, D, BN, LO::kRowBytes);
   if (rc == DFL_OK) rc = encode_tensor_map_3d(&tv, p.v, D, L, BH, row, seq, D, BN, LO::kRowBytes);
@@ -443,6 +542,7 @@ int launch_fused_typed(const DflAttnTablesParams& p, cudaStream_t stream) {
   const void* pq = p.pos_query ? p.pos_query : p.pos_key;
   if (rc == DFL_OK) rc = encode_tensor_map_3d(&tpk, pk, D, A, p.heads, row, table, D, BN, LO::kRowBytes);
   if (rc == DFL_OK) rc = encode_tensor_map_3d(&tpq, pq, D, A, p.heads, row, table, D, BM, LO::kRowBytes);
+  if (rc == DFL_OK) rc = encode_tensor_map_3d(&tpq64, pq, D, A, p.heads, row, table, D, BM / 2, LO::kRowBytes);
   if (rc != DFL_OK) return rc;
 
   constexpr int kMaxSmem = 232448;
@@ -465,7 +565,7 @@ int launch_fused_typed(const DflAttnTablesParams& p, cudaStream_t stream) {
   }
   dim3 grid((L + BM - 1) / BM, BH);
   if (grid.y > 65535) return fail(DFL_ERR_TOO_LARGE, "batch*heads > 65535");
-  kernel<<<grid, kThreads, smem_request, stream>>>(tq, tk, tv, tpk, tpq, p, status_word);
+  kernel<<<grid, kThreads, smem_request, stream>>>(tq, tk, tv, tpk, tpq, tpq64, p, status_word);
   return check_launch("attention_fused_kernel");
 }
 
@@ -473,7 +573,7 @@ int launch_fused_typed(const DflAttnTablesParams& p, cudaStream_t stream) {
 
 bool attention_fused_supported(const DflAttnTablesParams& p) {
   return p.dtype != DFL_F32 && (p.head_dim == 32 || p.head_dim == 64) && (p.pos_key || p.pos_query) &&
-         p.n_active >= 1 && p.n_active <= 992 && p.seq_len <= 2048;
+         p.n_active >= 1 && p.n_active <= 4096 && p.seq_len <= 1024;
 }
 
 int launch_attention_fused(const DflAttnTablesParams& p, cudaStream_t stream) {
@@ -485,3 +585,15 @@ int launch_attention_fused(const DflAttnTablesParams& p, cudaStream_t stream) {
 }
 
 }  // namespace dfl
+
+#ifdef DFL_TRACE
+extern "C" int dfl_debug_read_trace(long long* host_buf, int clear) {
+  cudaDeviceSynchronize();
+  cudaError_t e = cudaMemcpyFromSymbol(host_buf, dfl::g_trace, sizeof(long long) * 16 * 512);
+  if (clear) {
+    static long long zeros[16 * 512] = {0};
+    cudaMemcpyToSymbol(dfl::g_trace, zeros, sizeof(zeros));
+  }
+  return (int)e;
+}
+#endif

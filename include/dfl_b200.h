@@ -203,7 +203,7 @@ DFL_API size_t dfl_static_scratch_bytes(void);
  * consumed from shared memory, so the two [B,H,L,A] tensors are never written to or read from
  * global memory.  Replaces, in one launch, the two torch.matmul calls (kernel.py:574-585) and the
  * Triton kernel (kernel.py:137-429).  Covered: FP16/BF16, head_dim 32 or 64, at least one position
- * term, n_active <= 992, seq_len <= 2048; dfl_attention_tables_supported() tells, and other
+ * term, n_active <= 4096, seq_len <= 1024; dfl_attention_tables_supported() tells, and other
  * configurations return DFL_ERR_UNSUPPORTED (use dfl_pos_scores + dfl_attention_fwd for them).
  */
 DFL_API int dfl_attention_tables_supported(const DflAttnTablesParams* p);
