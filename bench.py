@@ -178,7 +178,19 @@ def cpu_encoder_seconds(cfg, backbone, hidden: torch.Tensor, mask: torch.Tensor)
     return time.perf_counter() - t0
 
 
+def use_all_host_threads() -> int:
+    """torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every core the job may use."""
+
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def cpu_baseline(layers: int, sample_batch: int, repeats: int, table: torch.Tensor):
+    use_all_host_threads()
     cfg, backbone = build_cpu_encoder(layers)
     batches = make_batches(1, sample_batch, WORKLOAD["seq_len"], 9000, table)
     hidden, mask = batches[0]
@@ -194,6 +206,7 @@ def run_reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    use_all_host_threads()
     table = embedding_table(17)
     cfg, backbone = build_cpu_encoder(args.layers)
     sample = args.cpu_sample

@@ -204,10 +204,13 @@ __device__ __forceinline__ bool softmax_part_tail(float (&s)[BN / PARTS], RowSta
   st.m_run = m_new;
   TRACE(52);
 
-  if (kt > 0) {
+  // O is rescaled only on the rare tiles where the reference maximum moved; only then does this thread
+  // have to see PV(kt-1) complete.  (The P buffer written below was last read by PV(kt-2), which is
+  // complete because S(kt), issued after it, has already been observed.)
+  if (kt > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {  // same decision in every warp of the row group
     if (!ptx::mbar_wait(o_ready, (uint32_t)(kt - 1) & 1u, abort_flag, status_word, 9)) return false;
     ptx::tc_fence_after();
-    if (__any_sync(0xffffffffu, corr != 1.0f)) {  // same decision in every warp of the row group
+    {
       uint32_t o[D / PARTS];
       tmem_ld_n(t_o_part, o);
       ptx::tmem_wait_ld();
