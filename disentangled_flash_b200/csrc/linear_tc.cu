@@ -9,14 +9,14 @@
 //
 //   C_z[m,n] = sum_k X_z[m,k] * W_{z % w_mod}[n,k] (+ bias[n]),  fp32 accumulation in TMEM
 //
-// One CTA computes one 128x128 output tile.  Warp 4 streams K-blocks of X and W
-// into a 3-stage shared-memory ring with TMA (128-byte swizzle, K-major),
-// warp 5 issues tcgen05.mma (M=128, N=128, K=16) from one elected thread into a
-// 128-column TMEM accumulator, warps 0-3 read the accumulator back with
-// tcgen05.ld (one row per thread), add the bias, round to the output type and
-// store 64-byte row segments either head-major [B,H,L,d] or row-major.  Two
-// CTAs fit per SM (2 x 97 KB shared memory, 2 x 128 TMEM columns), so one CTA's
-// epilogue overlaps the other's main loop.
+// Persistent kernel, one CTA per SM, each walking 128x256 output tiles.  Warp 4
+// streams K-blocks of X and W into a 4-stage shared-memory ring with TMA
+// (128-byte swizzle, K-major) and keeps streaming across tile boundaries,
+// warp 5 issues tcgen05.mma (M=128, N=256, K=16) from one elected thread into
+// one of two 256-column TMEM accumulators, warps 0-3 read the finished
+// accumulator back with tcgen05.ld (one row per thread), add the bias, round to
+// the output type and store 64-byte row segments either head-major [B,H,L,d] or
+// row-major -- while the MMA warp already fills the other accumulator.
 #include "dfl_common.cuh"
 #include "tcgen05_ptx.cuh"
 
@@ -68,10 +68,10 @@ __device__ int g_gemm_status = 0;
 
 namespace {
 
-constexpr int TM = 128, TN = 128;
-constexpr int STAGES = 3;
+constexpr int TM = 128, TN = 256;  // 128 x 256 output tile: 87 flop per operand byte staged through shared memory
 constexpr int kThreads = 192;
-constexpr int kTmemCols = 128;
+constexpr int kTmemCols = 512;      // two 256-column accumulators: epilogue of tile i overlaps main loop of tile i+1
+constexpr int kMaxSmem = 232448;
 
 template <int BK>
 struct GemmSmem {
@@ -79,32 +79,39 @@ struct GemmSmem {
   static constexpr int kTileA = TM * kRowBytes;
   static constexpr int kTileB = TN * kRowBytes;
   static constexpr int kStage = kTileA + kTileB;
-  static constexpr int kBarrierOffset = STAGES * kStage;
-  static constexpr int kTotal = kBarrierOffset + 256 + 1024;  // barriers + holder + flags, + alignment slack
+  static constexpr int kStages = BK == 64 ? 4 : 6;          // 192 KB / 144 KB of operand ring: one CTA per SM
+  static constexpr int kBarrierOffset = kStages * kStage;
+  static constexpr int kTotal = kBarrierOffset + 512 + 1024;  // barriers + holder + flags, + alignment slack
 };
 
+// Persistent kernel: grid = number of SMs (or fewer tiles); each CTA walks tiles t = blockIdx.x, + gridDim.x, ...
+// Tile order: n fastest, so that CTAs running concurrently share rows of X in L2.
 template <typename T, int BK>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-               const GemmDesc g, const int num_kb) {
+               const GemmDesc g, const int num_kb, const int tiles_n, const int tiles_m, const int num_tiles) {
   using S = GemmSmem<BK>;
+  constexpr int STAGES = S::kStages;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::kBarrierOffset);
   uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* tmem_full_bar = empty_bar + STAGES;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+  uint64_t* tmem_full_bar = empty_bar + STAGES;   // [2]
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;   // [2]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * TN, m0 = blockIdx.y * TM, z = blockIdx.z;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       ptx::mbar_init(&full_bar[s], 1);
       ptx::mbar_init(&empty_bar[s], 1);
     }
-    ptx::mbar_init(tmem_full_bar, 1);
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(&tmem_full_bar[a], 1);
+      ptx::mbar_init(&tmem_empty_bar[a], 4);  // one elected lane of each epilogue warp
+    }
     *abort_flag = 0;
     ptx::fence_mbar_init();
   }
@@ -121,90 +128,127 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
+  auto tile_coords = [&](int tile, int& m0, int& n0, int& z) {
+    const int per_z = tiles_n * tiles_m;
+    z = tile / per_z;
+    const int rem = tile - z * per_z;
+    const int tm = rem / tiles_n;
+    m0 = tm * TM;
+    n0 = (rem - tm * tiles_n) * TN;
+  };
+
   if (warp == 4) {
     // ---------------------------------------------------------- TMA producer
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, &g_gemm_status, 1)) break;
-        ptx::mbar_arrive_expect_tx(&full_bar[s], (uint32_t)S::kStage);
-        unsigned char* a = smem + s * S::kStage;
-        ptx::tma_load_3d(a, &tmap_x, &full_bar[s], kb * BK, m0, z);
-        ptx::tma_load_3d(a + S::kTileA, &tmap_w, &full_bar[s], kb * BK, n0, z % g.w_mod);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int m0, n0, z;
+        tile_coords(tile, m0, n0, z);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          ok = ptx::mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, &g_gemm_status, 1);
+          if (!ok) break;
+          ptx::mbar_arrive_expect_tx(&full_bar[s], (uint32_t)S::kStage);
+          unsigned char* a = smem + s * S::kStage;
+          ptx::tma_load_3d(a, &tmap_x, &full_bar[s], kb * BK, m0, z);
+          ptx::tma_load_3d(a + S::kTileA, &tmap_w, &full_bar[s], kb * BK, n0, z % g.w_mod);
+        }
       }
     }
   } else if (warp == 5) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = ptx::make_idesc_f16(sizeof(T) == 2 && !__is_same(T, __half) ? 1 : 0, TM, TN, 0, 0);
+      constexpr uint32_t idesc = ptx::make_idesc_f16(__is_same(T, __nv_bfloat16) ? 1 : 0, TM, TN, 0, 0);
       constexpr uint32_t mode = ptx::swizzle_mode_for_row_bytes(S::kRowBytes);
+      const uint64_t adesc0 = ptx::make_smem_desc(ptx::smem_u32(smem), 16, 8 * S::kRowBytes, mode);
+      const uint64_t bdesc0 = ptx::make_smem_desc(ptx::smem_u32(smem + S::kTileA), 16, 8 * S::kRowBytes, mode);
+      uint32_t it = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        ok = ptx::mbar_wait(&full_bar[s], ph, abort_flag, &g_gemm_status, 2);
+      int lt = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
+        const int acc = lt & 1;
+        ok = ptx::mbar_wait(&tmem_empty_bar[acc], ((uint32_t)(lt >> 1) & 1u) ^ 1u, abort_flag, &g_gemm_status, 4);
         if (!ok) break;
         ptx::tc_fence_after();
-        const uint32_t a_addr = ptx::smem_u32(smem + s * S::kStage);
-        const uint32_t b_addr = a_addr + S::kTileA;
+        const uint32_t d_tmem = tmem_base + acc * TN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          ok = ptx::mbar_wait(&full_bar[s], ph, abort_flag, &g_gemm_status, 2);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          // descriptors differ from the stage-0 ones only in the 16-byte-granular address field
+          const uint64_t adesc = adesc0 + (uint64_t)(s * (S::kStage >> 4));
+          const uint64_t bdesc = bdesc0 + (uint64_t)(s * (S::kStage >> 4));
 #pragma unroll
-        for (int k = 0; k < BK / 16; ++k) {
-          const uint64_t adesc = ptx::make_smem_desc(a_addr + k * 32, 16, 8 * S::kRowBytes, mode);
-          const uint64_t bdesc = ptx::make_smem_desc(b_addr + k * 32, 16, 8 * S::kRowBytes, mode);
-          ptx::umma_ss_f16(tmem_base, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < BK / 16; ++k)
+            ptx::umma_ss_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          ptx::umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
         }
-        ptx::umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+        if (!ok) break;
+        ptx::umma_commit(&tmem_full_bar[acc]);  // accumulator complete
       }
-      ptx::umma_commit(tmem_full_bar);    // accumulator complete
     }
   } else {
     // -------------------------------------------------------------- epilogue
-    const bool ready = ptx::mbar_wait(tmem_full_bar, 0, abort_flag, &g_gemm_status, 3);
-    ptx::tc_fence_after();
-    const int row = warp * 32 + lane;
-    const int m = m0 + row;
     const int ncols = g.head_split ? g.N : g.ldc;
     const T* bias = reinterpret_cast<const T*>(g.bias);
     const int hd = g.heads * g.head_dim;
+    bool ready = true;
+    int lt = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++lt) {
+      int m0, n0, z;
+      tile_coords(tile, m0, n0, z);
+      const int acc = lt & 1;
+      if (ready) ready = ptx::mbar_wait(&tmem_full_bar[acc], (uint32_t)(lt >> 1) & 1u, abort_flag, &g_gemm_status, 3);
+      ptx::tc_fence_after();
+      const int row = warp * 32 + lane;
+      const int m = m0 + row;
 #pragma unroll 1
-    for (int c0 = 0; c0 < TN; c0 += 32) {
-      const int n = n0 + c0;
-      if (n >= ncols) break;  // warp-uniform
-      uint32_t r[32];
-      ptx::tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
-      ptx::tmem_wait_ld();
-      if (!ready || m >= g.M) continue;
-      T* dst;
-      int valid = 32;
-      if (g.head_split) {
-        const int which = n / hd, rem = n - which * hd;
-        const int h = rem / g.head_dim, dd = rem - h * g.head_dim;
-        const int b = m / g.rows_per_seq, l = m - b * g.rows_per_seq;
-        T* out = reinterpret_cast<T*>(which == 0 ? g.out[0] : (which == 1 ? g.out[1] : g.out[2]));
-        dst = out + (((long long)b * g.heads + h) * g.rows_per_seq + l) * g.head_dim + dd;
-      } else {
-        dst = reinterpret_cast<T*>(g.out[0]) + (long long)z * g.stride_c + (long long)m * g.ldc + n;
-        valid = ncols - n < 32 ? ncols - n : 32;  // multiple of 8
-      }
-#pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        if (v * 8 >= valid) break;
-        float f[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
-        if (bias) {
-          const uint4 braw = __ldg(reinterpret_cast<const uint4*>(bias + n + v * 8));
-          const T* bh = reinterpret_cast<const T*>(&braw);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) f[j] += Elem<T>::to_f(bh[j]);
+      for (int c0 = 0; c0 < TN; c0 += 32) {
+        const int n = n0 + c0;
+        if (n >= ncols) break;  // warp-uniform
+        uint32_t r[32];
+        ptx::tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * TN + c0), r);
+        ptx::tmem_wait_ld();
+        if (!ready || m >= g.M) continue;
+        T* dst;
+        int valid = 32;
+        if (g.head_split) {
+          const int which = n / hd, rem = n - which * hd;
+          const int h = rem / g.head_dim, dd = rem - h * g.head_dim;
+          const int b = m / g.rows_per_seq, l = m - b * g.rows_per_seq;
+          T* out = reinterpret_cast<T*>(which == 0 ? g.out[0] : (which == 1 ? g.out[1] : g.out[2]));
+          dst = out + (((long long)b * g.heads + h) * g.rows_per_seq + l) * g.head_dim + dd;
+        } else {
+          dst = reinterpret_cast<T*>(g.out[0]) + (long long)z * g.stride_c + (long long)m * g.ldc + n;
+          valid = ncols - n < 32 ? ncols - n : 32;  // multiple of 8
         }
-        uint4 packed;
-        T* ph = reinterpret_cast<T*>(&packed);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ph[j] = Elem<T>::from_f(f[j]);
-        *reinterpret_cast<uint4*>(dst + v * 8) = packed;
+        for (int v = 0; v < 4; ++v) {
+          if (v * 8 >= valid) break;
+          float f[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+          if (bias) {
+            const uint4 braw = __ldg(reinterpret_cast<const uint4*>(bias + n + v * 8));
+            const T* bh = reinterpret_cast<const T*>(&braw);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] += Elem<T>::to_f(bh[j]);
+          }
+          uint4 packed;
+          T* ph = reinterpret_cast<T*>(&packed);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ph[j] = Elem<T>::from_f(f[j]);
+          *reinterpret_cast<uint4*>(dst + v * 8) = packed;
+        }
       }
+      // this warp has read its lanes of the accumulator: hand it back to the MMA issuer
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[acc]);
     }
   }
 
@@ -228,16 +272,23 @@ int launch_bk(const GemmDesc& g, cudaStream_t stream) {
 
   auto kernel = gemm_tc_kernel<T, BK>;
   static bool configured = false;  // per template instantiation
+  static int num_sms = 0;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "gemm_tc smem opt-in: %s", cudaGetErrorString(e));
+    int dev = 0;
+    cudaGetDevice(&dev);
+    e = cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess || num_sms < 1) return fail(DFL_ERR_LAUNCH, "SM count query failed");
     configured = true;
   }
   const int ncols = g.head_split ? g.N : g.ldc;
-  dim3 grid((ncols + TN - 1) / TN, (g.M + TM - 1) / TM, g.batch);
-  if (grid.y > 65535 || grid.z > 65535) return fail(DFL_ERR_TOO_LARGE, "gemm_tc grid too large");
+  const int tiles_n = (ncols + TN - 1) / TN, tiles_m = (g.M + TM - 1) / TM;
+  const long long num_tiles = (long long)tiles_n * tiles_m * g.batch;
+  if (num_tiles > 0x7fffffff) return fail(DFL_ERR_TOO_LARGE, "gemm_tc: too many tiles");
+  const int grid = (int)(num_tiles < num_sms ? num_tiles : num_sms);
   const int num_kb = (g.K + BK - 1) / BK;
-  kernel<<<grid, kThreads, S::kTotal, stream>>>(tmap_x, tmap_w, g, num_kb);
+  kernel<<<grid, kThreads, S::kTotal, stream>>>(tmap_x, tmap_w, g, num_kb, tiles_n, tiles_m, (int)num_tiles);
   return check_launch("gemm_tc_kernel");
 }
 
