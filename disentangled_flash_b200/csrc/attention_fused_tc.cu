@@ -113,13 +113,13 @@ struct FTables {
   const uint32_t* kbits;  // key keep-bits
 };
 
-// C2P block jobs of tile t: the first tile brings blocks hi>>6 .. lo>>6, later tiles at most one.
+// C2P block jobs of tile t: the first processed tile brings blocks hi>>6 .. lo>>6, later tiles at most one.
 struct BlockJobs {
   int first, count;  // blocks first, first-1, ..., first-count+1
 };
-__device__ __forceinline__ BlockJobs c2p_jobs(const FTables& tb, int t) {
+__device__ __forceinline__ BlockJobs c2p_jobs(const FTables& tb, int t, int t_begin) {
   const int blo = tb.win_lo[t] >> 6;
-  if (t == 0) return {tb.win_hi[0] >> 6, (tb.win_hi[0] >> 6) - blo + 1};
+  if (t == t_begin) return {tb.win_hi[t] >> 6, (tb.win_hi[t] >> 6) - blo + 1};
   const int prev = tb.win_lo[t - 1] >> 6;
   return {blo, blo < prev ? 1 : 0};
 }
@@ -195,23 +195,21 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     ptx::tmem_relinquish();
   }
   // slot tables, edge-replicated so that out-of-range (i, j) pairs resolve inside the tile's window
-  {
-    auto slot_at = [&](int e) {
-      int src = e - LUT_LO_PAD;
-      src = src < 0 ? 0 : (src > 2 * L - 2 ? 2 * L - 2 : src);
-      return (int)p.lut[src];
-    };
-    for (int e = threadIdx.x; e < n_lut; e += kThreads) {
-      uint32_t m = 0;
-      int cur = slot_at(e);
-      lutS[e] = (uint16_t)cur;
-      for (int x = 0; x < 31 && e - x - 1 >= 0; ++x) {
-        const int nxt = slot_at(e - x - 1);
-        m |= (uint32_t)(cur - nxt) << x;
-        cur = nxt;
-      }
-      stepM[e] = m;
+  for (int e = threadIdx.x; e < n_lut; e += kThreads) {
+    int src = e - LUT_LO_PAD;
+    src = src < 0 ? 0 : (src > 2 * L - 2 ? 2 * L - 2 : src);
+    lutS[e] = (uint16_t)p.lut[src];
+  }
+  __syncthreads();  // step masks are derived from the staged copy, not from global memory
+  for (int e = threadIdx.x; e < n_lut; e += kThreads) {
+    uint32_t m = 0;
+    int cur = lutS[e];
+    for (int x = 0; x < 31 && e - x - 1 >= 0; ++x) {
+      const int nxt = lutS[e - x - 1];
+      m |= (uint32_t)(cur - nxt) << x;
+      cur = nxt;
     }
+    stepM[e] = m;
   }
   for (int t = threadIdx.x; t < n_kt; t += kThreads) {
     int a = i0 - (t * BN + BN - 1) + (L - 1), z = i0 + (BM - 1) - t * BN + (L - 1);
@@ -226,10 +224,50 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     const uint32_t bits = __ballot_sync(0xffffffffu, keep);
     if (lane == 0) kbits[w] = bits;
   }
+  // Key tiles before the first and after the last kept key contribute nothing to a kept query row
+  // (their probabilities are exactly zero) and are skipped; a padded query row attends uniformly to all
+  // L keys, so a query tile that contains one walks every key tile.
+  const bool my_row_in_range = threadIdx.x < BM && i0 + (int)threadIdx.x < L;
+  const bool my_row_kept = my_row_in_range && mask_keep(p.mask, p.mask_elem_size, (long long)b * L + i0 + threadIdx.x);
   ptx::tc_fence_before();
-  __syncthreads();
+  const bool any_padded_row = __syncthreads_or(my_row_in_range && !my_row_kept) != 0;
+  const bool any_kept_row = __syncthreads_or(my_row_kept) != 0;
   ptx::tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  int t_begin = 0, t_end = n_kt;
+  if (!any_padded_row) {
+    while (t_begin < n_kt - 1 && (kbits[2 * t_begin] | kbits[2 * t_begin + 1]) == 0) ++t_begin;
+    while (t_end > t_begin + 1 && (kbits[2 * t_end - 2] | kbits[2 * t_end - 1]) == 0) --t_end;
+  }
+  const int n_tiles = t_end - t_begin;
+
+  if (!any_kept_row) {
+    // Every query row of this tile is padding: each of them attends uniformly to all L keys, so every
+    // output row is the column mean of V.  No score, no softmax: one pass over V by the whole CTA.
+    float* part = reinterpret_cast<float*>(smem + LO::offRing);   // [groups][D] partial sums, then [D] means
+    constexpr int kGroups = kThreads / D;
+    const int col = threadIdx.x % D, grp = threadIdx.x / D;
+    const T* V = reinterpret_cast<const T*>(p.v) + (long long)bh * L * D;
+    float sum = 0.0f;
+    if (grp < kGroups)
+      for (int row = grp; row < L; row += kGroups) sum += Elem<T>::to_f(V[(long long)row * D + col]);
+    if (grp < kGroups) part[grp * D + col] = sum;
+    __syncthreads();
+    T* mean = reinterpret_cast<T*>(part + kGroups * D);
+    if (threadIdx.x < D) {
+      float total = 0.0f;
+      for (int gidx = 0; gidx < kGroups; ++gidx) total += part[gidx * D + threadIdx.x];
+      mean[threadIdx.x] = Elem<T>::from_f(total / (float)L);
+    }
+    __syncthreads();
+    const int rows = L - i0 < BM ? L - i0 : BM;
+    constexpr int kVec = D / 8;  // 16-byte chunks per output row
+    T* out = reinterpret_cast<T*>(p.out) + ((long long)b * L + i0) * ((long long)H * D) + (long long)h * D;
+    for (int e = threadIdx.x; e < rows * kVec; e += kThreads) {
+      const int rr = e / kVec, v = e - rr * kVec;
+      *reinterpret_cast<uint4*>(out + (long long)rr * H * D + v * 8) = *reinterpret_cast<const uint4*>(mean + v * 8);
+    }
+  } else
 
   if (warp == kTmaWarp) {
     // ------------------------------------------------------------ TMA producer
@@ -238,9 +276,10 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       ptx::mbar_arrive_expect_tx(&bars->q_full, (uint32_t)LO::kQ);
       ptx::tma_load_3d(smem + LO::offQ, &tmap_q, &bars->q_full, 0, i0, bh);
       uint32_t n_job = 0;
-      for (int t = 0; t < n_kt && ok; ++t) {
+      for (int t = t_begin; t < t_end && ok; ++t) {
+        const int u = t - t_begin;  // ordinal of the tile among the processed ones: drives stages and parities
         if (has_c2p) {
-          const BlockJobs jobs = c2p_jobs(tb, t);
+          const BlockJobs jobs = c2p_jobs(tb, t, t_begin);
           for (int x = 0; x < jobs.count && ok; ++x, ++n_job) {
             ok = ptx::mbar_wait(&bars->pk_empty, (n_job & 1u) ^ 1u, abort_flag, status_word, 11);
             if (!ok) break;
@@ -250,7 +289,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           if (!ok) break;
         }
         if (has_p2c) {
-          ok = ptx::mbar_wait(&bars->pq_empty, ((uint32_t)t & 1u) ^ 1u, abort_flag, status_word, 12);
+          ok = ptx::mbar_wait(&bars->pq_empty, ((uint32_t)u & 1u) ^ 1u, abort_flag, status_word, 12);
           if (!ok) break;
           TRACE(32);
           const int lo = win_lo[t];
@@ -259,8 +298,8 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           ptx::tma_load_3d(smem + LO::offPQ, &tmap_pq, &bars->pq_full, 0, lo, h);
           if (two) ptx::tma_load_3d(smem + LO::offPQ + LO::kQ, &tmap_pq64, &bars->pq_full, 0, lo + 128, h);
         }
-        const int s = t % KV_STAGES;
-        ok = ptx::mbar_wait(&bars->kv_empty[s], ((uint32_t)(t / KV_STAGES) & 1u) ^ 1u, abort_flag, status_word, 1);
+        const int s = u % KV_STAGES;
+        ok = ptx::mbar_wait(&bars->kv_empty[s], ((uint32_t)(u / KV_STAGES) & 1u) ^ 1u, abort_flag, status_word, 1);
         if (!ok) break;
         TRACE(33);
         ptx::mbar_arrive_expect_tx(&bars->kv_full[s], (uint32_t)(2 * LO::kK));
@@ -297,7 +336,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       // everything tile t needs before its softmax: new C2P blocks, PT, S
       auto issue_front = [&](int t) -> bool {
         if (has_c2p) {
-          const BlockJobs jobs = c2p_jobs(tb, t);
+          const BlockJobs jobs = c2p_jobs(tb, t, t_begin);
           for (int x = 0; x < jobs.count; ++x, ++n_job) {
             if (!ptx::mbar_wait(&bars->pk_full, n_job & 1u, abort_flag, status_word, 13)) return false;
             if (!ptx::mbar_wait(&bars->cnew_free, (n_job & 1u) ^ 1u, abort_flag, status_word, 14)) return false;
@@ -308,13 +347,14 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             ptx::umma_commit(&bars->cnew_full);
           }
         }
-        const int s = t % KV_STAGES, sb = t & 1;
-        if (!ptx::mbar_wait(&bars->kv_full[s], (uint32_t)(t / KV_STAGES) & 1u, abort_flag, status_word, 3)) return false;
+        const int u = t - t_begin;
+        const int s = u % KV_STAGES, sb = u & 1;
+        if (!ptx::mbar_wait(&bars->kv_full[s], (uint32_t)(u / KV_STAGES) & 1u, abort_flag, status_word, 3)) return false;
         TRACE(23);
         const uint32_t k_addr = ptx::smem_u32(smem + LO::offKV + s * 2 * LO::kK);
         if (has_p2c) {
-          if (!ptx::mbar_wait(&bars->pq_full, (uint32_t)t & 1u, abort_flag, status_word, 15)) return false;
-          if (!ptx::mbar_wait(&bars->pt_free, ((uint32_t)t & 1u) ^ 1u, abort_flag, status_word, 16)) return false;
+          if (!ptx::mbar_wait(&bars->pq_full, (uint32_t)u & 1u, abort_flag, status_word, 15)) return false;
+          if (!ptx::mbar_wait(&bars->pt_free, ((uint32_t)u & 1u) ^ 1u, abort_flag, status_word, 16)) return false;
           TRACE(25);
           ptx::tc_fence_after();
           mma_128x64(COL_PT, pq_addr, k_addr);
@@ -322,7 +362,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           ptx::umma_commit(&bars->pq_empty);
           ptx::umma_commit(&bars->pt_full);
         }
-        if (!ptx::mbar_wait(&bars->s_free[sb], ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag, status_word, 4)) return false;
+        if (!ptx::mbar_wait(&bars->s_free[sb], ((uint32_t)(u >> 1) & 1u) ^ 1u, abort_flag, status_word, 4)) return false;
         TRACE(26);
         ptx::tc_fence_after();
         mma_128x64(COL_S + sb * BN, q_addr, k_addr);
@@ -330,12 +370,13 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         return true;
       };
 
-      if (ok) ok = issue_front(0);
-      for (int t = 0; t < n_kt && ok; ++t) {
-        if (t + 1 < n_kt) ok = issue_front(t + 1);
+      if (ok) ok = issue_front(t_begin);
+      for (int t = t_begin; t < t_end && ok; ++t) {
+        if (t + 1 < t_end) ok = issue_front(t + 1);
         if (!ok) break;
-        const int s = t % KV_STAGES, sb = t & 1;
-        ok = ptx::mbar_wait(&bars->p_full[sb], (uint32_t)(t >> 1) & 1u, abort_flag, status_word, 5);
+        const int u = t - t_begin;
+        const int s = u % KV_STAGES, sb = u & 1;
+        ok = ptx::mbar_wait(&bars->p_full[sb], (uint32_t)(u >> 1) & 1u, abort_flag, status_word, 5);
         if (!ok) break;
         TRACE(27);
         ptx::tc_fence_after();
@@ -344,7 +385,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         for (int kk = 0; kk < BN / 16; ++kk) {
           const uint64_t bdesc = ptx::make_smem_desc(v_addr + kk * 16 * LO::kRowBytes, LO::kK, sbo, mode);
           ptx::umma_ts_f16(tmem_base + COL_O, tmem_base + COL_P + sb * (BN / 2) + kk * 8, bdesc, idesc_pv,
-                           (t | kk) != 0 ? 1u : 0u);
+                           (u | kk) != 0 ? 1u : 0u);
         }
         ptx::umma_commit(&bars->kv_empty[s]);
         ptx::umma_commit(&bars->o_ready);
@@ -381,13 +422,14 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       }
     };
 
-    for (int t = 0; t < n_kt && ok; ++t) {
+    for (int t = t_begin; t < t_end && ok; ++t) {
+      const int u = t - t_begin;
       if (has_c2p) {
-        const BlockJobs jobs = c2p_jobs(tb, t);
+        const BlockJobs jobs = c2p_jobs(tb, t, t_begin);
         // The ring position a new block overwrites was last needed by tile t-2.  The wait is taken even
         // when tile t brings no block: it keeps this role at most two tiles ahead of the softmax, which the
         // two-phase c2p_ready barriers rely on.
-        ok = ptx::mbar_wait(&bars->ring_release[t & 1], ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag, status_word, 17);
+        ok = ptx::mbar_wait(&bars->ring_release[u & 1], ((uint32_t)(u >> 1) & 1u) ^ 1u, abort_flag, status_word, 17);
         if (!ok) break;
         TRACE(11);
         for (int x = 0; x < jobs.count && ok; ++x, ++n_job) {
@@ -406,15 +448,15 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         }
         if (!ok) break;
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&bars->c2p_ready[t & 1]);
+        if (lane == 0) ptx::mbar_arrive(&bars->c2p_ready[u & 1]);
       }
       if (has_p2c) {
-        ok = ptx::mbar_wait(&bars->pt_full, (uint32_t)t & 1u, abort_flag, status_word, 19);
+        ok = ptx::mbar_wait(&bars->pt_full, (uint32_t)u & 1u, abort_flag, status_word, 19);
         if (!ok) break;
         TRACE(14);
         ptx::tc_fence_after();
         // the staging tile is single-buffered: tile t-1 must have been gathered
-        ok = ptx::mbar_wait(&bars->pt_release, ((uint32_t)t & 1u) ^ 1u, abort_flag, status_word, 20);
+        ok = ptx::mbar_wait(&bars->pt_release, ((uint32_t)u & 1u) ^ 1u, abort_flag, status_word, 20);
         if (!ok) break;
         TRACE(15);
         convert_64(tmem_base + lane_base + COL_PT, pt_base + row * (PT_PITCH_H * 2));
@@ -446,9 +488,10 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     attn::RowState st;
     bool ok = true;
 
-    for (int t = 0; t < n_kt && ok; ++t) {
-      const int sb = t & 1, j0 = t * BN + part * W;  // first key of this thread's part
-      ok = ptx::mbar_wait(&bars->s_full[sb], (uint32_t)(t >> 1) & 1u, abort_flag, status_word, 7);
+    for (int t = t_begin; t < t_end && ok; ++t) {
+      const int u = t - t_begin;
+      const int sb = u & 1, j0 = t * BN + part * W;  // first key of this thread's part
+      ok = ptx::mbar_wait(&bars->s_full[sb], (uint32_t)(u >> 1) & 1u, abort_flag, status_word, 7);
       if (!ok) break;
       TRACE(1);
       ptx::tc_fence_after();
@@ -471,11 +514,11 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       const uint32_t steps = stepM[e0];
       const int s0 = lutS[e0];
       if (has_c2p) {
-        ok = ptx::mbar_wait(&bars->c2p_ready[sb], (uint32_t)(t >> 1) & 1u, abort_flag, status_word, 8);
+        ok = ptx::mbar_wait(&bars->c2p_ready[sb], (uint32_t)(u >> 1) & 1u, abort_flag, status_word, 8);
         if (!ok) break;
       }
       if (has_p2c) {
-        ok = ptx::mbar_wait(&bars->pt_ready, (uint32_t)t & 1u, abort_flag, status_word, 21);
+        ok = ptx::mbar_wait(&bars->pt_ready, (uint32_t)u & 1u, abort_flag, status_word, 21);
         if (!ok) break;
       }
       TRACE(3);
@@ -512,14 +555,14 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       TRACE(6);
 
       const uint32_t kb = kbits[(j0 >> 5)] >> (j0 & 31);
-      ok = attn::softmax_part_tail<T, D, kParts>(s, st, kb, L - j0, q_keep, cscale, t, part, r, xc, t_o_part,
+      ok = attn::softmax_part_tail<T, D, kParts>(s, st, kb, L - j0, q_keep, cscale, u, part, r, xc, t_o_part,
                                                  tmem_base + lane_base + COL_P + sb * (BN / 2) + part * (W / 2),
                                                  &bars->o_ready, &bars->p_full[sb], abort_flag, status_word TRACE_ARG);
       TRACE(7);
     }
     T* out = reinterpret_cast<T*>(p.out) + ((long long)b * L + (row_ok ? i : 0)) * ((long long)H * D) +
              (long long)h * D + part * (D / kParts);
-    attn::softmax_part_store<T, D, kParts>(st, ok, row_ok, n_kt, part, r, xc, t_o_part, out, &bars->o_ready,
+    attn::softmax_part_store<T, D, kParts>(st, ok, row_ok, n_tiles, part, r, xc, t_o_part, out, &bars->o_ready,
                                            abort_flag, status_word);
   }
 
