@@ -244,6 +244,30 @@ def workload_config(args, note: str | None = None):
     return cfg
 
 
+def executed_tile_fraction(mask: torch.Tensor, bm: int = 128, bn: int = 64) -> float:
+    """Fraction of (query tile, key tile) pairs the fused attention kernel actually computes for this mask.
+
+    Mirrors the kernel's rule: a 128-row query tile whose in-range rows are all padding takes the mean-of-V
+    path (no tile); a query tile with no padded row walks only the key tiles between the first and the last
+    kept key; a mixed query tile walks every key tile (padded rows attend to all L keys).
+    """
+
+    batch, length = mask.shape
+    n_q, n_k = -(-length // bm), -(-length // bn)
+    done = 0
+    for b in range(batch):
+        row = mask[b].bool()
+        kept_tiles = [bool(row[t * bn:(t + 1) * bn].any()) for t in range(n_k)]
+        first = kept_tiles.index(True) if any(kept_tiles) else 0
+        last = n_k - 1 - kept_tiles[::-1].index(True) if any(kept_tiles) else n_k - 1
+        for q in range(n_q):
+            rows = row[q * bm:(q + 1) * bm]
+            if not rows.any():
+                continue
+            done += n_k if not rows.all() else last - first + 1
+    return done / float(batch * n_q * n_k)
+
+
 # ----------------------------------------------------------------------------- GPU arm
 def run_gpu_arm(args) -> None:
     import torch.distributed as dist
@@ -332,13 +356,17 @@ def run_gpu_arm(args) -> None:
     e2e_value = seqs / (ms_e2e / 1e3)
 
     # Roofline of the dominant kernel: the fused attention forward (tensor-core bound by design).
+    # Only work the kernel does not skip is counted (key tiles outside the kept range and fully padded
+    # query tiles are skipped; see executed_tile_fraction).
     B, H, L, d = args.batch, WORKLOAD["heads"], WORKLOAD["seq_len"], WORKLOAD["head_dim"]
-    flops_attn = 4.0 * B * H * L * L * d  # QK^T + PV; the kernel skips no tile
     n_active = int(encoder._active_plans[0].active_slots.numel())
     in_kernel_scores = observer.kernel_name == "dfl_attention_tables_fwd"
+    used = [host_mask[i % len(host_mask)] for i in range(args.steps)]
+    executed = statistics.mean(executed_tile_fraction(m) for m in used) if in_kernel_scores else 1.0
+    flops_attn = 4.0 * B * H * L * L * d * executed  # QK^T + PV over the executed tiles
     # with the relative scores computed in-kernel, their non-redundant GEMM work (2 terms, A active slots)
-    # is part of the launch; window MMAs executed beyond that are not counted
-    flops_pos = 2.0 * 2 * B * H * L * n_active * d if in_kernel_scores else 0.0
+    # is part of the launch, in the same proportion; window MMAs executed beyond that are not counted
+    flops_pos = 2.0 * 2 * B * H * L * n_active * d * executed if in_kernel_scores else 0.0
     flops_per_launch = flops_attn + flops_pos
     attn_avg_ms = statistics.mean(attn_ms) if attn_ms else float("nan")
     achieved = flops_per_launch / (attn_avg_ms * 1e-3) / 1e12
@@ -349,7 +377,8 @@ def run_gpu_arm(args) -> None:
                 "peak_source": f"{peak_kind} cuBLAS bf16 sustained (kernel timed inside a long step)",
                 "avg_launch_ms": attn_avg_ms, "launches_timed": len(attn_ms),
                 "algorithmic_flops_per_launch": flops_per_launch,
-                "flops_qk_pv": flops_attn, "flops_position_scores": flops_pos}
+                "flops_qk_pv": flops_attn, "flops_position_scores": flops_pos,
+                "executed_tile_fraction": executed}
 
     checks = sharding.gather_for_check(checksum)  # NCCL only here, after timing, for checking
     if rank == 0:

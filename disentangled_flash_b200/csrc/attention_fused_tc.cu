@@ -79,11 +79,12 @@ struct FLayout {
   static constexpr int kBarBytes = 512;
   static constexpr int offXchg = offBar + kBarBytes;            // row exchange: [2][kParts][BM] floats
   static constexpr int offTables = offXchg + 2 * kParts * BM * 4;
-  // tables: stepM u32[n_lut], lutS u16[n_lut], win_lo/win_hi int16[n_kt] each, kbits u32[2*n_kt]
+  // tables: step bits u32[n_lut/32 + 2], lutS u16[n_lut], win_lo/win_hi int16[n_kt] each, kbits u32[2*n_kt]
+  static __host__ __device__ constexpr int wbits_bytes(int n_lut) { return (((n_lut + 31) / 32 + 1) * 4 + 15) & ~15; }
   static int total(int L) {
     const int n_lut = 2 * L - 1 + LUT_LO_PAD + LUT_HI_PAD;
     const int n_kt = (L + BN - 1) / BN;
-    return offTables + ((6 * n_lut + 15) & ~15) + ((4 * n_kt + 15) & ~15) + 8 * n_kt + 1024;
+    return offTables + wbits_bytes(n_lut) + ((2 * n_lut + 15) & ~15) + ((4 * n_kt + 15) & ~15) + 8 * n_kt + 1024;
   }
 };
 
@@ -106,7 +107,7 @@ struct FBarriers {
 static_assert(sizeof(FBarriers) <= 512, "barrier block too large");
 
 struct FTables {
-  const uint32_t* stepM;  // bit x of entry e: slot(e - x) - slot(e - x - 1), x = 0..30 (slot steps are 0 or 1)
+  const uint32_t* wbits;  // step bits: bit l of word k+1 is slot(32k+l) - slot(32k+l-1) (0 or 1); word 0 is zero
   const uint16_t* lutS;   // slot of each (padded) delta index
   const int16_t* win_lo;  // per key tile: lowest slot touched
   const int16_t* win_hi;  // per key tile: highest slot touched
@@ -144,13 +145,14 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   const bool has_c2p = p.pos_key != nullptr, has_p2c = p.pos_query != nullptr;
   const int n_lut = 2 * L - 1 + LUT_LO_PAD + LUT_HI_PAD;
   TRACE_DECL
+  TRACE(99);
 
-  uint32_t* stepM = reinterpret_cast<uint32_t*>(smem + LO::offTables);
-  uint16_t* lutS = reinterpret_cast<uint16_t*>(stepM + n_lut);
-  int16_t* win_lo = reinterpret_cast<int16_t*>(smem + LO::offTables + ((6 * n_lut + 15) & ~15));
+  uint32_t* wbits = reinterpret_cast<uint32_t*>(smem + LO::offTables);          // [(n_lut+31)/32 + 1]
+  uint16_t* lutS = reinterpret_cast<uint16_t*>(smem + LO::offTables + LO::wbits_bytes(n_lut));
+  int16_t* win_lo = reinterpret_cast<int16_t*>(smem + LO::offTables + LO::wbits_bytes(n_lut) + ((2 * n_lut + 15) & ~15));
   int16_t* win_hi = win_lo + n_kt;
-  uint32_t* kbits = reinterpret_cast<uint32_t*>(smem + LO::offTables + ((6 * n_lut + 15) & ~15) + ((4 * n_kt + 15) & ~15));
-  const FTables tb{stepM, lutS, win_lo, win_hi, kbits};
+  uint32_t* kbits = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(win_lo) + ((4 * n_kt + 15) & ~15));
+  const FTables tb{wbits, lutS, win_lo, win_hi, kbits};
 
   // ------------------------------------------------------------------ setup
   if (threadIdx.x == 0) {
@@ -194,30 +196,15 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     ptx::tmem_alloc(&bars->tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
-  // slot tables, edge-replicated so that out-of-range (i, j) pairs resolve inside the tile's window
+  TRACE(97);
+  // ---- tables.  All global reads are issued first; two block-wide syncs follow.
+  // slot table, edge-replicated so that out-of-range (i, j) pairs resolve inside the tile's window
   for (int e = threadIdx.x; e < n_lut; e += kThreads) {
     int src = e - LUT_LO_PAD;
     src = src < 0 ? 0 : (src > 2 * L - 2 ? 2 * L - 2 : src);
     lutS[e] = (uint16_t)p.lut[src];
   }
-  __syncthreads();  // step masks are derived from the staged copy, not from global memory
-  for (int e = threadIdx.x; e < n_lut; e += kThreads) {
-    uint32_t m = 0;
-    int cur = lutS[e];
-    for (int x = 0; x < 31 && e - x - 1 >= 0; ++x) {
-      const int nxt = lutS[e - x - 1];
-      m |= (uint32_t)(cur - nxt) << x;
-      cur = nxt;
-    }
-    stepM[e] = m;
-  }
-  for (int t = threadIdx.x; t < n_kt; t += kThreads) {
-    int a = i0 - (t * BN + BN - 1) + (L - 1), z = i0 + (BM - 1) - t * BN + (L - 1);
-    a = a < 0 ? 0 : (a > 2 * L - 2 ? 2 * L - 2 : a);
-    z = z < 0 ? 0 : (z > 2 * L - 2 ? 2 * L - 2 : z);
-    win_lo[t] = (int16_t)p.lut[a];
-    win_hi[t] = (int16_t)p.lut[z];
-  }
+  // key keep-mask as bits: word w covers keys [32w, 32w+32); keys >= L are 0
   for (int w = warp; w < 2 * n_kt; w += kThreads / 32) {
     const int j = w * 32 + lane;
     const bool keep = j < L && mask_keep(p.mask, p.mask_elem_size, (long long)b * L + j);
@@ -230,7 +217,28 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   const bool my_row_in_range = threadIdx.x < BM && i0 + (int)threadIdx.x < L;
   const bool my_row_kept = my_row_in_range && mask_keep(p.mask, p.mask_elem_size, (long long)b * L + i0 + threadIdx.x);
   ptx::tc_fence_before();
+  TRACE(96);
   const bool any_padded_row = __syncthreads_or(my_row_in_range && !my_row_kept) != 0;
+  TRACE(95);
+  // step bit of entry e: slot(e) - slot(e-1) (0 or 1).  One ballot per 32 entries stores them in entry order;
+  // a softmax thread later takes the 32-bit window that ends at its entry (see step_mask_at).
+  {
+    const int n_words = (n_lut + 31) / 32;
+    for (int k = warp; k < n_words; k += kThreads / 32) {
+      const int e = k * 32 + lane;
+      const bool step = e >= 1 && e < n_lut && lutS[e] != lutS[e - 1];
+      const uint32_t bits = __ballot_sync(0xffffffffu, step);
+      if (lane == 0) wbits[k + 1] = bits;
+    }
+    if (threadIdx.x == 0) wbits[0] = 0;
+  }
+  for (int t = threadIdx.x; t < n_kt; t += kThreads) {
+    int a = i0 - (t * BN + BN - 1) + (L - 1), z = i0 + (BM - 1) - t * BN + (L - 1);
+    a = a < 0 ? 0 : (a > 2 * L - 2 ? 2 * L - 2 : a);
+    z = z < 0 ? 0 : (z > 2 * L - 2 ? 2 * L - 2 : z);
+    win_lo[t] = (int16_t)lutS[a + LUT_LO_PAD];
+    win_hi[t] = (int16_t)lutS[z + LUT_LO_PAD];
+  }
   const bool any_kept_row = __syncthreads_or(my_row_kept) != 0;
   ptx::tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
@@ -240,6 +248,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     while (t_end > t_begin + 1 && (kbits[2 * t_end - 2] | kbits[2 * t_end - 1]) == 0) --t_end;
   }
   const int n_tiles = t_end - t_begin;
+  TRACE(98);
 
   if (!any_kept_row) {
     // Every query row of this tile is padding: each of them attends uniformly to all L keys, so every
@@ -482,8 +491,8 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     const float cscale = p.scale * 1.4426950408889634f;
     const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
     const uint32_t t_o_part = tmem_base + lane_base + COL_O + part * (D / kParts);
-    const uint16_t* ring_row = reinterpret_cast<const uint16_t*>(smem + LO::offRing) + r * RING_PITCH_H;
-    const uint16_t* pt16 = reinterpret_cast<const uint16_t*>(smem + LO::offPT);
+    const uint32_t ring_addr = ptx::smem_u32(smem + LO::offRing) + (uint32_t)(r * RING_PITCH_H * 2);
+    const uint32_t pt_addr = ptx::smem_u32(smem + LO::offPT);
     const attn::RowExchange xc{reinterpret_cast<float*>(smem + LO::offXchg), &bars->pair[q4]};
     attn::RowState st;
     bool ok = true;
@@ -511,7 +520,8 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       // Slots of this thread's W pairs: s_0 = slot(i, j0) and s_{x+1} = s_x - step bit x (steps are 0 or 1), so the
       // two gathers walk their row with a running address instead of one table lookup per element.
       const int e0 = LUT_LO_PAD + i - j0 + (L - 1);  // table index of pair (i, j0); pair (i, j0+x) is e0 - x
-      const uint32_t steps = stepM[e0];
+      // bit x of steps = slot(e0 - x) - slot(e0 - x - 1): the bit-reversed 32-entry window ending at e0
+      const uint32_t steps = __brev(__funnelshift_rc(wbits[e0 >> 5], wbits[(e0 >> 5) + 1], (e0 & 31) + 1)) & 0x7fffffffu;
       const int s0 = lutS[e0];
       if (has_c2p) {
         ok = ptx::mbar_wait(&bars->c2p_ready[sb], (uint32_t)(u >> 1) & 1u, abort_flag, status_word, 8);
@@ -524,18 +534,19 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       TRACE(3);
       {
         // C2P: ring position of slot s0; the mirror makes pos-(W-1) .. pos contiguous.
-        int cidx = s0 % RING_SPAN;
-        if (cidx < W - 1) cidx += RING_SPAN;
+        int pos = s0 % RING_SPAN;
+        if (pos < W - 1) pos += RING_SPAN;
+        uint32_t caddr = ring_addr + 2u * (uint32_t)pos;
         // P2C: PT[slot - lo][key]; the row moves down one pitch whenever the slot steps, the column follows x.
-        int pidx = (s0 - (int)win_lo[t]) * PT_PITCH_H + part * W;
+        uint32_t paddr = pt_addr + (uint32_t)((s0 - (int)win_lo[t]) * (PT_PITCH_H * 2) + part * W * 2);
         uint16_t cval[W], pval[W];
 #pragma unroll
         for (int x = 0; x < W; ++x) {
-          if (has_c2p) cval[x] = ring_row[cidx];
-          if (has_p2c) pval[x] = pt16[pidx + x];
+          if (has_c2p) cval[x] = ptx::lds_u16(caddr);
+          if (has_p2c) pval[x] = ptx::lds_u16(paddr + 2u * x);
           if (steps & (1u << x)) {
-            cidx -= 1;
-            pidx -= PT_PITCH_H;
+            caddr -= 2u;
+            paddr -= (uint32_t)(PT_PITCH_H * 2);
           }
         }
         if (has_c2p) {

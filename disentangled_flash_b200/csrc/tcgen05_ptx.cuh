@@ -106,11 +106,11 @@ __device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t* bar) {
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-// Shared-memory 16-bit load by 32-bit shared address.  Volatile keeps a batch of these in program
-// order (and after the preceding barrier wait) while the hardware overlaps them.
+// Shared-memory 16-bit load by 32-bit shared address.  The "memory" clobber keeps the compiler from moving
+// the load above the barrier wait that makes the data visible; the hardware still overlaps a batch of them.
 __device__ __forceinline__ uint16_t lds_u16(uint32_t saddr) {
   uint16_t v;
-  asm volatile("ld.volatile.shared.u16 %0, [%1];" : "=h"(v) : "r"(saddr) : "memory");
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(saddr) : "memory");
   return v;
 }
 
