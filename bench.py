@@ -380,6 +380,39 @@ def run_gpu_arm(args) -> None:
                 "flops_qk_pv": flops_attn, "flops_position_scores": flops_pos,
                 "executed_tile_fraction": executed}
 
+    # The attention operator alone on unpadded inputs (the shape the tensor-core target is quoted on): kernel timed
+    # in isolation, L2 flushed between launches, against the burst peak.
+    attention_op = None
+    if rank == 0:
+        plan0 = encoder._active_plans[0]
+        gen = torch.Generator().manual_seed(5)
+        q, k, v = (torch.randn(B, H, L, d, generator=gen).to(dtype).to(device) for _ in range(3))
+        full = torch.ones(B, L, dtype=torch.bool, device=device)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+        scale = 1.0 / (3.0 * d) ** 0.5
+        call = lambda: _cabi.attention_tables_fwd(q, k, v, plan0.pos_key, plan0.pos_query, plan0.delta_to_local,  # noqa: E731
+                                                  full, scale)
+        with torch.inference_mode():
+            for _ in range(3):
+                call()
+            times = []
+            for _ in range(10):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                call()
+                e1.record()
+                torch.cuda.synchronize()
+                times.append(e0.elapsed_time(e1))
+        op_ms = statistics.median(times)
+        op_flops = 4.0 * B * H * L * L * d + 2.0 * 2 * B * H * L * n_active * d
+        burst = float(peaks.get("bf16_tflops") or peak)
+        attention_op = {"config": f"B={B} H={H} L={L} d={d} fp16, no padding, c2p+p2c computed in-kernel",
+                        "us_per_launch": op_ms * 1e3, "tflops": op_flops / (op_ms * 1e-3) / 1e12,
+                        "frac_of_burst_peak": op_flops / (op_ms * 1e-3) / 1e12 / burst,
+                        "flops_qk_pv": 4.0 * B * H * L * L * d, "l2": "256 MB flush write between launches"}
+        del q, k, v, flush
+
     checks = sharding.gather_for_check(checksum)  # NCCL only here, after timing, for checking
     if rank == 0:
         baseline = cpu_baseline(args.layers, args.cpu_sample, 3, table) if world == 1 and not args.skip_cpu else None
@@ -395,6 +428,7 @@ def run_gpu_arm(args) -> None:
             "gpu_launches": observer.launches,
             "attention_tflops": achieved,
             "roofline": roofline,
+            "attention_op": attention_op,
             "cpu_baseline": baseline,
             "clocks": clocks,
             "rank_checksums": [float(c.item()) for c in checks],

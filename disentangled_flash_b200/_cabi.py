@@ -43,6 +43,9 @@ EXPORTED_SYMBOLS = (
     "dfl_static_scratch_bytes",
     "dfl_attention_tables_supported",
     "dfl_attention_tables_fwd",
+    "dfl_expand_rel_tables",
+    "dfl_attention_rel_supported",
+    "dfl_attention_rel_fwd",
 )
 
 
@@ -80,6 +83,15 @@ class DflAttnTablesParams(Structure):
         ("batch", c_int32), ("heads", c_int32), ("seq_len", c_int32), ("head_dim", c_int32),
         ("n_active", c_int32), ("mask_elem_size", c_int32), ("scale", c_float),
         ("dtype", c_int32), ("algo", c_int32),
+    ]
+
+
+class DflAttnRelParams(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("rel_key", c_void_p), ("rel_query", c_void_p),
+        ("mask", c_void_p), ("out", c_void_p), ("status", c_void_p),
+        ("batch", c_int32), ("heads", c_int32), ("seq_len", c_int32), ("head_dim", c_int32),
+        ("mask_elem_size", c_int32), ("scale", c_float), ("dtype", c_int32), ("algo", c_int32),
     ]
 
 
@@ -151,6 +163,12 @@ def load_library() -> ctypes.CDLL:
     lib.dfl_attention_tables_supported.argtypes = [POINTER(DflAttnTablesParams)]
     lib.dfl_attention_tables_fwd.restype = c_int
     lib.dfl_attention_tables_fwd.argtypes = [POINTER(DflAttnTablesParams), c_void_p]
+    lib.dfl_expand_rel_tables.restype = c_int
+    lib.dfl_expand_rel_tables.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    lib.dfl_attention_rel_supported.restype = c_int
+    lib.dfl_attention_rel_supported.argtypes = [POINTER(DflAttnRelParams)]
+    lib.dfl_attention_rel_fwd.restype = c_int
+    lib.dfl_attention_rel_fwd.argtypes = [POINTER(DflAttnRelParams), c_void_p]
     _lib = lib
     return lib
 
@@ -361,4 +379,60 @@ def attention_tables_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_
     p = _tables_params(q, k, v, pos_key, pos_query, lut, mask, scale, out, ALGO_AUTO, status)
     with torch.cuda.device(q.device), _observe("dfl_attention_tables_fwd", 1):
         _check(lib.dfl_attention_tables_fwd(ctypes.byref(p), _stream(q.device)), "dfl_attention_tables_fwd")
+    return out
+
+
+def expand_rel_tables(pos: torch.Tensor, lut: torch.Tensor, seq_len: int) -> torch.Tensor:
+    """Pruned table ``pos`` [H, A, d] -> ``rel`` [H, 2L-1, d], rel[h, e] = pos[h, lut[2L-2-e]] (prepare-time)."""
+
+    lib = load_library()
+    _require_cuda_contiguous("pos", pos)
+    _require_cuda_contiguous("lut", lut)
+    if lut.dtype != torch.int32 or lut.numel() != 2 * seq_len - 1:
+        raise ValueError("lut must be int32 [2L-1]")
+    heads, n_active, d = pos.shape
+    rel = torch.empty(heads, 2 * seq_len - 1, d, dtype=pos.dtype, device=pos.device)
+    with torch.cuda.device(pos.device), _observe("dfl_expand_rel_tables", 1):
+        _check(lib.dfl_expand_rel_tables(pos.data_ptr(), lut.data_ptr(), rel.data_ptr(), heads, n_active, seq_len, d,
+                                         dtype_code(pos.dtype), _stream(pos.device)), "dfl_expand_rel_tables")
+    return rel
+
+
+def attention_rel_supported(q: torch.Tensor, has_c2p: bool, has_p2c: bool, algo: int = ALGO_AUTO) -> bool:
+    """Whether ``attention_rel_fwd`` covers this configuration (shape and dtype of ``q``, enabled terms)."""
+
+    if not (has_c2p or has_p2c) or algo != ALGO_AUTO:
+        return False
+    p = DflAttnRelParams()
+    # only nullness of the table pointers is inspected
+    p.rel_key, p.rel_query = (1 if has_c2p else None), (1 if has_p2c else None)
+    p.batch, p.heads, p.seq_len, p.head_dim = q.shape
+    p.dtype, p.algo = dtype_code(q.dtype), algo
+    return bool(load_library().dfl_attention_rel_supported(ctypes.byref(p)))
+
+
+def attention_rel_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rel_key: torch.Tensor | None,
+                      rel_query: torch.Tensor | None, mask: torch.Tensor, scale: float, *,
+                      status: torch.Tensor | None = None) -> torch.Tensor:
+    """Fused attention over position tables laid out by relative distance ([H, 2L-1, d])."""
+
+    lib = load_library()
+    for name, t in (("q", q), ("k", k), ("v", v), ("mask", mask)):
+        _require_cuda_contiguous(name, t)
+    bsz, heads, length, d = q.shape
+    for name, t in (("rel_key", rel_key), ("rel_query", rel_query)):
+        if t is not None:
+            _require_cuda_contiguous(name, t)
+            if t.shape != (heads, 2 * length - 1, d) or t.dtype != q.dtype:
+                raise ValueError(f"{name} must be [H, 2L-1, d] in the dtype of q")
+    if mask.element_size() not in (1, 4, 8) or mask.dtype.is_floating_point:
+        raise TypeError("mask must be a bool or integer tensor")
+    out = torch.empty(bsz, length, heads * d, dtype=q.dtype, device=q.device)
+    p = DflAttnRelParams()
+    p.q, p.k, p.v, p.rel_key, p.rel_query = q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(rel_key), _ptr(rel_query)
+    p.mask, p.out, p.status = mask.data_ptr(), out.data_ptr(), _ptr(status)
+    p.batch, p.heads, p.seq_len, p.head_dim = bsz, heads, length, d
+    p.mask_elem_size, p.scale, p.dtype, p.algo = mask.element_size(), scale, dtype_code(q.dtype), ALGO_AUTO
+    with torch.cuda.device(q.device), _observe("dfl_attention_rel_fwd", 1):
+        _check(lib.dfl_attention_rel_fwd(ctypes.byref(p), _stream(q.device)), "dfl_attention_rel_fwd")
     return out

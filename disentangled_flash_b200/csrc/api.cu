@@ -162,4 +162,34 @@ int dfl_attention_tables_fwd(const DflAttnTablesParams* p, void* stream) {
   return launch_attention_fused(*p, (cudaStream_t)stream);
 }
 
+int dfl_expand_rel_tables(const void* pos, const int32_t* lut_dev, void* rel, int heads, int n_active, int seq_len,
+                          int head_dim, int dtype, void* stream) {
+  if (!valid_dtype(dtype)) return fail(DFL_ERR_BAD_ARG, "unknown dtype %d", dtype);
+  if (heads < 1 || n_active < 1 || seq_len < 1 || head_dim < 1) return fail(DFL_ERR_BAD_ARG, "non-positive size");
+  if (!pos || !lut_dev || !rel) return fail(DFL_ERR_BAD_ARG, "null pointer");
+  if ((head_dim * dtype_size(dtype)) % 16) return fail(DFL_ERR_ALIGNMENT, "table rows must be multiples of 16 bytes");
+  if (!aligned16(pos) || !aligned16(rel)) return fail(DFL_ERR_ALIGNMENT, "table not 16-byte aligned");
+  return launch_expand_rel_tables(pos, lut_dev, rel, heads, n_active, seq_len, head_dim, dtype, (cudaStream_t)stream);
+}
+
+int dfl_attention_rel_supported(const DflAttnRelParams* p) {
+  return p && p->algo == DFL_ALGO_AUTO && attention_rel_supported(*p) ? 1 : 0;
+}
+
+int dfl_attention_rel_fwd(const DflAttnRelParams* p, void* stream) {
+  if (!p) return fail(DFL_ERR_BAD_ARG, "null params");
+  if (!valid_dtype(p->dtype)) return fail(DFL_ERR_BAD_ARG, "unknown dtype %d", p->dtype);
+  if (p->batch < 1 || p->heads < 1 || p->seq_len < 1) return fail(DFL_ERR_BAD_ARG, "non-positive size");
+  if (!p->q || !p->k || !p->v || !p->out || !p->mask) return fail(DFL_ERR_BAD_ARG, "null pointer");
+  if (p->mask_elem_size != 1 && p->mask_elem_size != 4 && p->mask_elem_size != 8)
+    return fail(DFL_ERR_BAD_ARG, "mask_elem_size must be 1, 4 or 8");
+  if (!(p->scale > 0.0f)) return fail(DFL_ERR_BAD_ARG, "scale must be positive");
+  if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out) ||
+      (p->rel_key && !aligned16(p->rel_key)) || (p->rel_query && !aligned16(p->rel_query)))
+    return fail(DFL_ERR_ALIGNMENT, "attention tensor not 16-byte aligned");
+  if (!dfl_attention_rel_supported(p))
+    return fail(DFL_ERR_UNSUPPORTED, "not covered by the relative-table kernel; use dfl_pos_scores + dfl_attention_fwd");
+  return launch_attention_rel(*p, (cudaStream_t)stream);
+}
+
 }  // extern "C"

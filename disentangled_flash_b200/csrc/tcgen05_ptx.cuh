@@ -78,6 +78,27 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return mbar_wait_slow(bar, parity, abort_flag, gstatus, code);
 }
 
+// Fully inlined bounded wait, for kernels that change their register budget with setmaxnreg (such kernels
+// cannot contain calls to separately compiled device functions).
+__device__ __forceinline__ bool mbar_wait_inline(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* gstatus,
+                                                 int code) {
+  unsigned long long t0 = 0;
+#pragma unroll 1
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 255u) {
+      if (*abort_flag) return false;
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (gstatus) atomicCAS(gstatus, 0, code);   // the first wait that gave up is the informative one
+        return false;
+      }
+    }
+  }
+}
+
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA / tcgen05)
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

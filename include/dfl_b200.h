@@ -209,6 +209,42 @@ DFL_API size_t dfl_static_scratch_bytes(void);
 DFL_API int dfl_attention_tables_supported(const DflAttnTablesParams* p);
 DFL_API int dfl_attention_tables_fwd(const DflAttnTablesParams* p, void* stream);
 
+/*
+ * Fused attention over position tables laid out by relative distance.
+ *
+ * dfl_expand_rel_tables() is a prepare-time step (once per layer and sequence length, next to the
+ * pruning of kernel.py:503-532): it expands a pruned table pos [H,A,d] through the slot table
+ * lut [2L-1] into rel [H, 2L-1, d] with rel[h, e] = pos[h, lut[2L-2-e]], i.e. row e holds the
+ * projection used by every (query i, key j) pair with j - i = e - (L-1).  No arithmetic: rows are copied.
+ *
+ * dfl_attention_rel_fwd() is the whole attention core in one launch, equal in result to
+ * dfl_pos_scores + dfl_attention_fwd (the two torch.matmul calls kernel.py:574-585 followed by the Triton
+ * kernel kernel.py:137-429): S = QK^T + q_i.rel_key[j-i] + k_j.rel_query[j-i], the two relative terms
+ * rounded to the input type as the separate score GEMMs round their output, scale, 2-D padding mask,
+ * softmax, PV.  The score tensors [B,H,L,A] never exist in global memory.  A persistent kernel: one CTA
+ * per SM walks (batch, head, 128-query-tile) items.  Covered: FP16/BF16, head_dim 32 or 64, at least one
+ * relative term, seq_len <= 1024; dfl_attention_rel_supported() tells, other configurations return
+ * DFL_ERR_UNSUPPORTED (use dfl_pos_scores + dfl_attention_fwd for them).
+ */
+typedef struct DflAttnRelParams {
+  const void* q;          /* [B,H,L,d] */
+  const void* k;          /* [B,H,L,d] */
+  const void* v;          /* [B,H,L,d] */
+  const void* rel_key;    /* [H,2L-1,d] expanded pos_key table, or NULL (C2P disabled) */
+  const void* rel_query;  /* [H,2L-1,d] expanded pos_query table, or NULL (P2C disabled) */
+  const void* mask;       /* [B,L] */
+  void*       out;        /* [B,L,H*d] */
+  int32_t*    status;     /* optional device int32, as in DflAttnParams */
+  int32_t batch, heads, seq_len, head_dim;
+  int32_t mask_elem_size; /* 1, 4 or 8 */
+  float   scale;
+  int32_t dtype, algo;
+} DflAttnRelParams;
+DFL_API int dfl_expand_rel_tables(const void* pos, const int32_t* lut_dev, void* rel, int heads, int n_active,
+                                  int seq_len, int head_dim, int dtype, void* stream);
+DFL_API int dfl_attention_rel_supported(const DflAttnRelParams* p);
+DFL_API int dfl_attention_rel_fwd(const DflAttnRelParams* p, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
