@@ -141,7 +141,7 @@ class LaunchObserver:
         if not self.enabled:
             return None
         self.launches += n_kernels
-        if name not in ("dfl_attention_fwd", "dfl_attention_tables_fwd"):
+        if name not in ("dfl_attention_fwd", "dfl_attention_rel_fwd"):
             return None
         self.kernel_name = name
         observer = self
@@ -360,7 +360,7 @@ def run_gpu_arm(args) -> None:
     # query tiles are skipped; see executed_tile_fraction).
     B, H, L, d = args.batch, WORKLOAD["heads"], WORKLOAD["seq_len"], WORKLOAD["head_dim"]
     n_active = int(encoder._active_plans[0].active_slots.numel())
-    in_kernel_scores = observer.kernel_name == "dfl_attention_tables_fwd"
+    in_kernel_scores = observer.kernel_name == "dfl_attention_rel_fwd"
     used = [host_mask[i % len(host_mask)] for i in range(args.steps)]
     executed = statistics.mean(executed_tile_fraction(m) for m in used) if in_kernel_scores else 1.0
     flops_attn = 4.0 * B * H * L * L * d * executed  # QK^T + PV over the executed tiles
@@ -390,8 +390,7 @@ def run_gpu_arm(args) -> None:
         full = torch.ones(B, L, dtype=torch.bool, device=device)
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
         scale = 1.0 / (3.0 * d) ** 0.5
-        call = lambda: _cabi.attention_tables_fwd(q, k, v, plan0.pos_key, plan0.pos_query, plan0.delta_to_local,  # noqa: E731
-                                                  full, scale)
+        call = lambda: _cabi.attention_rel_fwd(q, k, v, plan0.rel_key, plan0.rel_query, full, scale)  # noqa: E731
         with torch.inference_mode():
             for _ in range(3):
                 call()

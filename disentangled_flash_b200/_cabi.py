@@ -41,8 +41,6 @@ EXPORTED_SYMBOLS = (
     "dfl_attention_fwd",
     "dfl_attention_fwd_static",
     "dfl_static_scratch_bytes",
-    "dfl_attention_tables_supported",
-    "dfl_attention_tables_fwd",
     "dfl_expand_rel_tables",
     "dfl_attention_rel_supported",
     "dfl_attention_rel_fwd",
@@ -159,10 +157,6 @@ def load_library() -> ctypes.CDLL:
     lib.dfl_attention_fwd_static.restype = c_int
     lib.dfl_attention_fwd_static.argtypes = [POINTER(DflAttnTablesParams), c_void_p]
     lib.dfl_static_scratch_bytes.restype = ctypes.c_size_t
-    lib.dfl_attention_tables_supported.restype = c_int
-    lib.dfl_attention_tables_supported.argtypes = [POINTER(DflAttnTablesParams)]
-    lib.dfl_attention_tables_fwd.restype = c_int
-    lib.dfl_attention_tables_fwd.argtypes = [POINTER(DflAttnTablesParams), c_void_p]
     lib.dfl_expand_rel_tables.restype = c_int
     lib.dfl_expand_rel_tables.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
     lib.dfl_attention_rel_supported.restype = c_int
@@ -352,36 +346,6 @@ def attention_fwd_static(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_
     return out
 
 
-def attention_tables_supported(q: torch.Tensor, pos_key: torch.Tensor | None, pos_query: torch.Tensor | None,
-                               algo: int = ALGO_AUTO) -> bool:
-    """Whether ``attention_tables_fwd`` (scores computed in-kernel) covers this configuration."""
-
-    table = pos_key if pos_key is not None else pos_query
-    if table is None or algo != ALGO_AUTO:
-        return False
-    p = DflAttnTablesParams()
-    p.pos_key, p.pos_query = _ptr(pos_key), _ptr(pos_query)
-    p.batch, p.heads, p.seq_len, p.head_dim = q.shape
-    p.n_active, p.dtype, p.algo = table.shape[1], dtype_code(q.dtype), algo
-    return bool(load_library().dfl_attention_tables_supported(ctypes.byref(p)))
-
-
-def attention_tables_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_key: torch.Tensor | None,
-                         pos_query: torch.Tensor | None, lut: torch.Tensor, mask: torch.Tensor, scale: float, *,
-                         status: torch.Tensor | None = None) -> torch.Tensor:
-    """Fused attention with the C2P/P2C scores computed inside the kernel from the position tables."""
-
-    lib = load_library()
-    for name, t in (("q", q), ("k", k), ("v", v), ("mask", mask), ("lut", lut)):
-        _require_cuda_contiguous(name, t)
-    bsz, heads, length, d = q.shape
-    out = torch.empty(bsz, length, heads * d, dtype=q.dtype, device=q.device)
-    p = _tables_params(q, k, v, pos_key, pos_query, lut, mask, scale, out, ALGO_AUTO, status)
-    with torch.cuda.device(q.device), _observe("dfl_attention_tables_fwd", 1):
-        _check(lib.dfl_attention_tables_fwd(ctypes.byref(p), _stream(q.device)), "dfl_attention_tables_fwd")
-    return out
-
-
 def expand_rel_tables(pos: torch.Tensor, lut: torch.Tensor, seq_len: int) -> torch.Tensor:
     """Pruned table ``pos`` [H, A, d] -> ``rel`` [H, 2L-1, d], rel[h, e] = pos[h, lut[2L-2-e]] (prepare-time)."""
 
@@ -398,16 +362,17 @@ def expand_rel_tables(pos: torch.Tensor, lut: torch.Tensor, seq_len: int) -> tor
     return rel
 
 
-def attention_rel_supported(q: torch.Tensor, has_c2p: bool, has_p2c: bool, algo: int = ALGO_AUTO) -> bool:
-    """Whether ``attention_rel_fwd`` covers this configuration (shape and dtype of ``q``, enabled terms)."""
+def attention_rel_supported(dtype: torch.dtype, seq_len: int, head_dim: int, has_c2p: bool, has_p2c: bool,
+                            algo: int = ALGO_AUTO) -> bool:
+    """Whether ``attention_rel_fwd`` covers this configuration."""
 
     if not (has_c2p or has_p2c) or algo != ALGO_AUTO:
         return False
     p = DflAttnRelParams()
     # only nullness of the table pointers is inspected
     p.rel_key, p.rel_query = (1 if has_c2p else None), (1 if has_p2c else None)
-    p.batch, p.heads, p.seq_len, p.head_dim = q.shape
-    p.dtype, p.algo = dtype_code(q.dtype), algo
+    p.batch, p.heads, p.seq_len, p.head_dim = 1, 1, seq_len, head_dim
+    p.dtype, p.algo = dtype_code(dtype), algo
     return bool(load_library().dfl_attention_rel_supported(ctypes.byref(p)))
 
 

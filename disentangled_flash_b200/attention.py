@@ -12,10 +12,10 @@ The hot function is :meth:`forward_prepared`.  On the current CUDA stream it
 issues ``dfl_qkv_proj`` (fused QKV projection, written head-major
 ``[B,H,L,d]``) followed by
 
-* ``dfl_attention_tables_fwd`` where it applies (FP16/BF16, head dim 32/64):
-  one kernel that computes the C2P/P2C scores over the pruned active slots
-  on the tensor cores and consumes them in place (QK^T + relative gathers +
-  mask + softmax + PV), or otherwise
+* ``dfl_attention_rel_fwd`` where it applies (FP16/BF16, head dim 32/64,
+  length up to 1024): one persistent kernel that computes the C2P/P2C scores
+  on the tensor cores from the plan's relative-distance tables and consumes
+  them in place (QK^T + relative gathers + mask + softmax + PV), or otherwise
 * ``dfl_pos_scores`` (the two score GEMMs) and ``dfl_attention_fwd`` (the
   fused kernel fed with their output), the reference's operator boundary.
 
@@ -49,12 +49,18 @@ class B200PreparedPositionPlan(NamedTuple):
     delta_to_local: torch.Tensor
     pos_key: torch.Tensor | None
     pos_query: torch.Tensor | None
+    # B200 additions: the pruned tables expanded by relative distance, [H, 2L-1, d], when the
+    # single-launch attention kernel covers the configuration (else None)
+    rel_key: torch.Tensor | None = None
+    rel_query: torch.Tensor | None = None
 
 
 # --------------------------------------------------------------------------
 # Operator boundary.  The reference registers its fused kernel as a torch
 # custom op so that torch.compile can trace the encoder around it
-# (kernel.py:431-438); this op plays the same role for the three C-ABI calls.
+# (kernel.py:431-438); this op plays the same role for the C-ABI calls of one layer:
+# dfl_qkv_proj, then dfl_attention_rel_fwd where the plan carries relative-distance
+# tables, else dfl_pos_scores + dfl_attention_fwd.
 # --------------------------------------------------------------------------
 @torch.library.custom_op("disentangled_flash_b200::attention_forward", mutates_args=(), device_types="cuda")
 def _attention_forward_op(
@@ -65,6 +71,8 @@ def _attention_forward_op(
     pos_key: Optional[torch.Tensor],
     pos_query: Optional[torch.Tensor],
     delta_to_local: Optional[torch.Tensor],
+    rel_key: Optional[torch.Tensor],
+    rel_query: Optional[torch.Tensor],
     num_heads: int,
     head_dim: int,
     scale: float,
@@ -75,9 +83,9 @@ def _attention_forward_op(
         hidden_states, qkv_weight, qkv_bias, n_out=3, heads=num_heads, head_dim=head_dim, rows_per_seq=length,
         algo=algo,
     )
-    if _cabi.attention_tables_supported(query, pos_key, pos_query, algo):
+    if rel_key is not None or rel_query is not None:
         # relative scores are produced inside the attention kernel: no [B,H,L,A] tensor in memory
-        return _cabi.attention_tables_fwd(query, key, value, pos_key, pos_query, delta_to_local, attention_mask, scale)
+        return _cabi.attention_rel_fwd(query, key, value, rel_key, rel_query, attention_mask, scale)
     c2p = p2c = None
     ld_slots = 0
     if pos_key is not None or pos_query is not None:
@@ -88,7 +96,7 @@ def _attention_forward_op(
 
 @_attention_forward_op.register_fake
 def _attention_forward_fake(hidden_states, attention_mask, qkv_weight, qkv_bias, pos_key, pos_query,
-                            delta_to_local, num_heads, head_dim, scale, algo):
+                            delta_to_local, rel_key, rel_query, num_heads, head_dim, scale, algo):
     return hidden_states.new_empty(hidden_states.shape[0], hidden_states.shape[1], num_heads * head_dim)
 
 
@@ -297,12 +305,22 @@ class DisentangledFlashAttention(nn.Module):
             return cached
         indices = self.position_plan_cache.compact(sequence_length, resolved)
         pos_key, pos_query = self._project_active_positions(indices.active_slots)
+        rel_key = rel_query = None
+        dtype = self.query_proj.weight.dtype
+        if _cabi.attention_rel_supported(dtype, sequence_length, self.attention_head_size, self.has_c2p, self.has_p2c,
+                                         self._algo):
+            if pos_key is not None:
+                rel_key = _cabi.expand_rel_tables(pos_key, indices.delta_to_local, sequence_length)
+            if pos_query is not None:
+                rel_query = _cabi.expand_rel_tables(pos_query, indices.delta_to_local, sequence_length)
         plan = B200PreparedPositionPlan(
             sequence_length=sequence_length,
             active_slots=indices.active_slots,
             delta_to_local=indices.delta_to_local,
             pos_key=pos_key,
             pos_query=pos_query,
+            rel_key=rel_key,
+            rel_query=rel_query,
         )
         self._position_projection_cache[key] = plan
         return plan
@@ -363,6 +381,8 @@ class DisentangledFlashAttention(nn.Module):
             plan.pos_key if self.has_c2p else None,
             plan.pos_query if self.has_p2c else None,
             plan.delta_to_local if uses_lut else None,
+            plan.rel_key if self.has_c2p else None,
+            plan.rel_query if self.has_p2c else None,
             self.num_attention_heads,
             self.attention_head_size,
             1.0 / self._scale(scale_factor),

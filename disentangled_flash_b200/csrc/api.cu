@@ -142,26 +142,6 @@ int dfl_attention_fwd(const DflAttnParams* p, void* stream) {
   return launch_attention_simt(*p, (cudaStream_t)stream);
 }
 
-int dfl_attention_tables_supported(const DflAttnTablesParams* p) {
-  return p && p->algo == DFL_ALGO_AUTO && attention_fused_supported(*p) ? 1 : 0;
-}
-
-int dfl_attention_tables_fwd(const DflAttnTablesParams* p, void* stream) {
-  if (!p) return fail(DFL_ERR_BAD_ARG, "null params");
-  if (!valid_dtype(p->dtype)) return fail(DFL_ERR_BAD_ARG, "unknown dtype %d", p->dtype);
-  if (p->batch < 1 || p->heads < 1 || p->seq_len < 1) return fail(DFL_ERR_BAD_ARG, "non-positive size");
-  if (!p->q || !p->k || !p->v || !p->out || !p->mask || !p->lut) return fail(DFL_ERR_BAD_ARG, "null pointer");
-  if (p->mask_elem_size != 1 && p->mask_elem_size != 4 && p->mask_elem_size != 8)
-    return fail(DFL_ERR_BAD_ARG, "mask_elem_size must be 1, 4 or 8");
-  if (!(p->scale > 0.0f)) return fail(DFL_ERR_BAD_ARG, "scale must be positive");
-  if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out) ||
-      (p->pos_key && !aligned16(p->pos_key)) || (p->pos_query && !aligned16(p->pos_query)))
-    return fail(DFL_ERR_ALIGNMENT, "attention tensor not 16-byte aligned");
-  if (!dfl_attention_tables_supported(p))
-    return fail(DFL_ERR_UNSUPPORTED, "not covered by the in-kernel score path; use dfl_pos_scores + dfl_attention_fwd");
-  return launch_attention_fused(*p, (cudaStream_t)stream);
-}
-
 int dfl_expand_rel_tables(const void* pos, const int32_t* lut_dev, void* rel, int heads, int n_active, int seq_len,
                           int head_dim, int dtype, void* stream) {
   if (!valid_dtype(dtype)) return fail(DFL_ERR_BAD_ARG, "unknown dtype %d", dtype);

@@ -19,10 +19,10 @@
 //   warps 0-3   softmax stream 0: one thread per query row, key tiles 0, 2, 4, ... of the item
 //   warps 4-7   softmax stream 1: key tiles 1, 3, 5, ...  Each stream has its own running maximum, row sum and
 //               output accumulator in TMEM (no per-tile exchange); the two are merged once per item.
-//   warps 8-11  converters: TMEM -> 16-bit -> shared memory for the C2P blocks and PT rows 0..127
-//   warps 12-13 converters for PT rows 128..191 (TMEM lanes 0..63 of the second accumulator)
+//   warps 8-11  converters: TMEM -> 16-bit -> shared memory for the C2P blocks and the PT tiles
+//   warps 12-13 PV issuers, one per stream: O[g] (+)= P[g] V as soon as the stream has stored P
 //   warp 14     per-item mask analysis (kept-key bits, skipped key tiles) and TMA producer
-//   warp 15     MMA issuer and TMEM owner
+//   warp 15     issuer of the "front" MMAs of a tile (new C2P block, PT, S) and TMEM owner
 #include <type_traits>
 
 #include "attention_tc_common.cuh"
@@ -38,8 +38,8 @@ using attn::BN;
 using attn::Pack2;
 
 constexpr int kSoftmaxWarps = 8;
-constexpr int kConvWarp0 = 8;
-constexpr int kConvHiWarp0 = 12;
+constexpr int kConvHiWarp0 = 12;      // end of the converter warps
+constexpr int kPvWarp0 = 12;
 constexpr int kTmaWarp = 14;
 constexpr int kMmaWarp = 15;
 constexpr int kThreads = 512;
@@ -90,7 +90,7 @@ struct RLayout {
 struct ItemSlot {
   int t_begin, t_end;   // key tiles [t_begin, t_end) are processed
   int any_kept;         // 0: every query row of the tile is padding -> mean-of-V path, no pipeline work
-  int pad;
+  int bh, i0;           // batch*heads + head, first query row
   uint32_t kbits[32];   // kept-key bits of the batch row, word w = keys [32w, 32w+32)
 };
 static_assert(sizeof(ItemSlot) <= 160, "item slot too large");
@@ -160,6 +160,51 @@ struct GatherAdd<T, N, N, STRIDE> {
   static __device__ __forceinline__ void run(float*, uint32_t) {}
 };
 
+// Kept-key bits of batch row b: lane w returns word w (keys [32w, 32w+32)) built from its own 32 mask elements.
+__device__ __forceinline__ uint32_t kept_bits_word(const DflAttnRelParams& p, int b, int lane) {
+  const int L = p.seq_len;
+  uint32_t kb = 0;
+  const int jw = 32 * lane;
+  const long long base = (long long)b * L + jw;
+  if (jw + 32 <= L && p.mask_elem_size == 1 && ((reinterpret_cast<uintptr_t>(p.mask) + base) & 15) == 0) {
+    const uint4* m16 = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(p.mask) + base);
+    const uint4 lo = m16[0], hi = m16[1];
+    const uint32_t wds[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+    for (int x = 0; x < 32; ++x)
+      if ((wds[x >> 2] >> ((x & 3) * 8)) & 0xffu) kb |= 1u << x;
+  } else if (jw < L) {
+#pragma unroll 8
+    for (int x = 0; x < 32; ++x)
+      if (jw + x < L && mask_keep(p.mask, p.mask_elem_size, base + x)) kb |= 1u << x;
+  }
+  return kb;
+}
+
+// Key tiles before the first and after the last kept key contribute nothing to a kept query row (their
+// probabilities are exactly zero) and are skipped; a padded query row attends uniformly to all L keys, so a query
+// tile that contains one walks every key tile.  A tile of padded rows only is the column mean of V (any_kept false).
+// Warp-collective: kb_mine is the lane's kept-key word of the batch row.
+struct TileRange {
+  int t_begin, t_end;
+  bool any_kept;
+};
+__device__ __forceinline__ TileRange tile_range(uint32_t kb_mine, int i0, int L, int lane) {
+  const int n_kt = (L + BN - 1) / BN;
+  const uint32_t nz = __ballot_sync(0xffffffffu, kb_mine != 0u);
+  const bool in_q = lane >= (i0 >> 5) && lane < (i0 >> 5) + BM / 32;
+  const int rows_here = L - 32 * lane;   // in-range rows of this lane's word
+  const uint32_t full = rows_here >= 32 ? 0xffffffffu : (rows_here <= 0 ? 0u : ((1u << rows_here) - 1u));
+  const bool any_kept = __ballot_sync(0xffffffffu, in_q && kb_mine != 0u) != 0u;
+  const bool any_padded = __ballot_sync(0xffffffffu, in_q && (kb_mine & full) != full) != 0u;
+  TileRange r{0, n_kt, any_kept};
+  if (!any_padded && nz != 0u) {
+    r.t_begin = (__ffs(nz) - 1) >> 1;
+    r.t_end = ((31 - __clz(nz)) >> 1) + 1;
+  }
+  return r;
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -175,8 +220,6 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 
   const int L = p.seq_len, H = p.heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_bh = p.batch * H;   // item = query tile * (batch*heads) + batch*head: a CTA's items differ in query tile
-  const int n_kt = (L + BN - 1) / BN;
   const bool has_c2p = p.rel_key != nullptr, has_p2c = p.rel_query != nullptr;
   TRACE_DECL
 
@@ -197,7 +240,7 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       ptx::mbar_init(&bars->o_ready[s], 1);
       ptx::mbar_init(&bars->c2p_ready[s], 4);     // converter warps 8-11
       ptx::mbar_init(&bars->ring_release[s], 4);
-      ptx::mbar_init(&bars->pt_ready[s], 6);      // converter warps 8-13
+      ptx::mbar_init(&bars->pt_ready[s], 4);      // converter warps 8-11
       ptx::mbar_init(&bars->pt_release[s], 4);
       ptx::mbar_init(&bars->item_full[s], 1);
       ptx::mbar_init(&bars->item_empty[s], 15);   // every warp but the loader
@@ -209,7 +252,7 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     ptx::mbar_init(&bars->cnew_full, 1);
     ptx::mbar_init(&bars->cnew_free, 4);
     ptx::mbar_init(&bars->pt_full, 1);
-    ptx::mbar_init(&bars->pt_free, 6);
+    ptx::mbar_init(&bars->pt_free, 4);
     ptx::mbar_init(&bars->xbar_a, kSoftmaxWarps);
     ptx::mbar_init(&bars->xbar_b, kSoftmaxWarps);
     bars->abort_flag = 0;
@@ -226,6 +269,9 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     ptx::tmem_alloc(&bars->tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
+  // Item order: item = query tile * (batch*heads) + batch*head, so the items of one CTA (stride gridDim) differ in
+  // query tile and batch row, which evens out the padding-dependent cost without any bookkeeping.
+  const int n_bh = p.batch * H;
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
@@ -236,11 +282,10 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 
   // Register budgets are set per warpgroup (warps 0-3, 4-7: softmax; 8-11: converters; 12-15: the rest), at the
   // head of the branch the whole warpgroup takes.
-  auto converter_role = [&](auto hi_tag) {
+  auto converter_role = [&]() {
     // -------------------------------------------------------------- converters
-    // Warps 8-11: thread (quarter q4, lane) owns TMEM lane 32*q4 + lane: a query row of a C2P block, a table row
-    // of the first PT accumulator.  Warps 12-13: lanes 0..63 of the second PT accumulator.
-    constexpr bool hi = decltype(hi_tag)::value;
+    // Thread (quarter q4, lane) owns TMEM lane 32*q4 + lane: a query row of a C2P block, a table row of the first
+    // PT accumulator and, for lanes 0..63 (warps 8 and 9), a table row of the second PT accumulator.
     const int q4 = warp & 3;
     const int row = q4 * 32 + lane;
     const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
@@ -276,7 +321,7 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       for (int u = 0; u < n && ok && any_kept; ++u) {
         const int g = u & 1;
         const uint32_t c_t = g ? c_t1 : c_t0;
-        if (has_c2p && !hi) {
+        if (has_c2p) {
           // The ring position a new block overwrites was last read by the stream's previous tile; the first tile of
           // an item also overwrites positions the other stream's last tile of the previous item read.
           ok = ptx::mbar_wait_inline(&bars->ring_release[g], (c_t & 1u) ^ 1u, abort_flag, status_word, 17);
@@ -310,13 +355,9 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           TRACE(15);
           const int pp = c_win & 3;
           unsigned char* stage = smem + LO::offPT + g * LO::kPTStage;
-          if (!hi) {
-            const int r0 = pp == 3 ? 64 : 0;
-            convert_64(tmem_base + lane_base + COL_PT, stage + (r0 + row) * (PT_PITCH_H * 2), false);
-          } else {
-            const int r0 = pp == 3 ? 0 : 128;
-            convert_64(tmem_base + lane_base + COL_PT + BN, stage + (r0 + row) * (PT_PITCH_H * 2), false);
-          }
+          convert_64(tmem_base + lane_base + COL_PT, stage + ((pp == 3 ? 64 : 0) + row) * (PT_PITCH_H * 2), false);
+          if (q4 < 2)
+            convert_64(tmem_base + lane_base + COL_PT + BN, stage + ((pp == 3 ? 0 : 128) + row) * (PT_PITCH_H * 2), false);
           ptx::tc_fence_before();
           __syncwarp();
           if (lane == 0) {
@@ -331,6 +372,49 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       }
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&bars->item_empty[slot]);
+    }
+  };
+
+  // Warps 12, 13 (lane 0): PV issuer of stream 0 / 1: O[g] (+)= P[g] . V(tile) once the stream's four warps have stored P.
+  auto pv_role = [&]() {
+    if (lane != 0) return;
+    const int g = warp - kPvWarp0;
+    constexpr int is_bf16 = __is_same(T, __nv_bfloat16) ? 1 : 0;
+    constexpr uint32_t idesc_pv = ptx::make_idesc_f16(is_bf16, BM, D, 0, 1);   // V is MN-major
+    constexpr uint32_t desc_hi = (((8u * LO::kRowBytes) >> 4) & 0x3FFFu) | (1u << 14) |
+                                 (ptx::swizzle_mode_for_row_bytes(LO::kRowBytes) << 29);
+    constexpr uint32_t kStepUnits = (16u * LO::kRowBytes) >> 4;   // 16 keys further down the V tile
+    const uint32_t v_lo = ((ptx::smem_u32(smem + LO::offV) >> 4) & 0x3FFFu) | (((uint32_t)LO::kBlk >> 4) << 16);
+    const uint32_t t_o = tmem_base + COL_O + g * 64, t_p = tmem_base + COL_P + g * (BN / 2);
+    uint32_t c_t = 0, c_tiles0 = 0;   // tiles of this stream so far; tiles of all earlier items
+    bool ok = true;
+    int k = 0;
+    for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++k) {
+      const int slot = k & 1;
+      ok = ptx::mbar_wait_inline(&bars->item_full[slot], (uint32_t)(k >> 1) & 1u, abort_flag, status_word, 36);
+      if (!ok) break;
+      const ItemSlot* sl = &slots[slot];
+      if (sl->any_kept != 0) {
+        const int n = sl->t_end - sl->t_begin;
+        for (int u = g; u < n && ok; u += 2, ++c_t) {
+          const uint32_t tile = c_tiles0 + (uint32_t)u, vb = tile & 1u;
+          ok = ptx::mbar_wait_inline(&bars->p_full[g], c_t & 1u, abort_flag, status_word, 7) &&
+               ptx::mbar_wait_inline(&bars->v_full[vb], (tile >> 1) & 1u, abort_flag, status_word, 8);
+          if (!ok) break;
+          TRACE(27);
+          ptx::tc_fence_after();
+          const uint32_t vt_lo = v_lo + vb * ((uint32_t)LO::kBlk >> 4);
+          if (u < 2) umma_ts_lohi<0>(t_o, t_p, vt_lo, desc_hi, idesc_pv);
+          else umma_ts_lohi<1>(t_o, t_p, vt_lo, desc_hi, idesc_pv);
+#pragma unroll
+          for (int kk = 1; kk < BN / 16; ++kk)
+            umma_ts_lohi<1>(t_o, t_p + kk * 8, vt_lo + kk * kStepUnits, desc_hi, idesc_pv);
+          ptx::umma_commit(&bars->v_empty[vb]);
+          ptx::umma_commit(&bars->o_ready[g]);
+        }
+        c_tiles0 += (uint32_t)n;
+      }
+      ptx::mbar_arrive(&bars->item_empty[slot]);
     }
   };
 
@@ -362,8 +446,8 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       const ItemSlot* sl = &slots[slot];
       const int t_begin = sl->t_begin, n = sl->t_end - sl->t_begin;
       const bool any_kept = sl->any_kept != 0;
-      const int qt = it / n_bh, bh = it - qt * n_bh, b = bh / H, h = bh - b * H;
-      const int i0 = qt * BM;
+      const int bh = sl->bh, b = bh / H, h = bh - b * H;
+      const int i0 = sl->i0;
 
       if (!any_kept) {
         // Every query row of this tile is padding: each attends uniformly to all L keys, so every output row is
@@ -575,11 +659,11 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     }
   } else if (warp < kConvHiWarp0) {
     setmaxnreg_dec();
-    converter_role(std::false_type{});
+    converter_role();
   } else {
     setmaxnreg_dec();
     if (warp < kTmaWarp) {
-      converter_role(std::true_type{});
+      pv_role();
     } else if (warp == kTmaWarp) {
     // ------------------------------------------------- mask analysis + TMA producer
     uint32_t c_q = 0, c_kv = 0, c_pk = 0, c_fq = 0;   // running counts: Q loads, K/V tiles, rel_key / rel_query blocks
@@ -593,43 +677,17 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       TRACE(40);
       ok = ptx::mbar_wait_inline(&bars->item_empty[slot], ((uint32_t)(k >> 1) & 1u) ^ 1u, abort_flag, status_word, 30);
       if (!ok) break;
-      // kept-key bits of batch row b: lane w builds word w (keys [32w, 32w+32)) from its own 32 mask elements
-      uint32_t kb_mine = 0;
-      {
-        const int jw = 32 * lane;
-        const long long base = (long long)b * L + jw;
-        if (jw + 32 <= L && p.mask_elem_size == 1 && ((reinterpret_cast<uintptr_t>(p.mask) + base) & 15) == 0) {
-          const uint4* m16 = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(p.mask) + base);
-          const uint4 lo = m16[0], hi = m16[1];
-          const uint32_t wds[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-#pragma unroll
-          for (int x = 0; x < 32; ++x)
-            if ((wds[x >> 2] >> ((x & 3) * 8)) & 0xffu) kb_mine |= 1u << x;
-        } else if (jw < L) {
-#pragma unroll 8
-          for (int x = 0; x < 32; ++x)
-            if (jw + x < L && mask_keep(p.mask, p.mask_elem_size, base + x)) kb_mine |= 1u << x;
-        }
-      }
-      // Key tiles before the first and after the last kept key contribute nothing to a kept query row (their
-      // probabilities are exactly zero) and are skipped; a padded query row attends uniformly to all L keys, so a
-      // query tile that contains one walks every key tile.  A tile of padded rows only is the column mean of V.
-      const uint32_t nz = __ballot_sync(0xffffffffu, kb_mine != 0u);
-      const bool in_q = lane >= (i0 >> 5) && lane < (i0 >> 5) + BM / 32;
-      const int rows_here = L - 32 * lane;   // in-range rows of this lane's word
-      const uint32_t full = rows_here >= 32 ? 0xffffffffu : (rows_here <= 0 ? 0u : ((1u << rows_here) - 1u));
-      const bool any_kept = __ballot_sync(0xffffffffu, in_q && kb_mine != 0u) != 0u;
-      const bool any_padded = __ballot_sync(0xffffffffu, in_q && (kb_mine & full) != full) != 0u;
-      int t_begin = 0, t_end = n_kt;
-      if (!any_padded && nz != 0u) {
-        t_begin = (__ffs(nz) - 1) >> 1;
-        t_end = ((31 - __clz(nz)) >> 1) + 1;
-      }
+      const uint32_t kb_mine = kept_bits_word(p, b, lane);
+      const TileRange range = tile_range(kb_mine, i0, L, lane);
+      const int t_begin = range.t_begin, t_end = range.t_end;
+      const bool any_kept = range.any_kept;
       sl->kbits[lane] = kb_mine;
       if (lane == 0) {
         sl->t_begin = t_begin;
         sl->t_end = t_end;
         sl->any_kept = any_kept ? 1 : 0;
+        sl->bh = bh;
+        sl->i0 = i0;
       }
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&bars->item_full[slot]);
@@ -695,14 +753,11 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     }
     } else {
     // -------------------------------------------------------------- MMA issuer
-    // One thread issues every MMA, so its instruction count per tile bounds the tile rate: descriptors are kept as
-    // precomputed 32-bit halves (only the start-address field moves), and the issue order is flattened over items:
-    // the "front" of a tile (new C2P block(s), PT, S) runs three tiles ahead of the PV of a tile, also across the
-    // boundary between two items, so that an item's first tiles are prepared while the previous item finishes.
+    // One thread issues the "front" of every tile (new C2P block(s), PT, S), so its instruction count per tile bounds
+    // the tile rate: descriptors are kept as precomputed 32-bit halves (only the start-address field moves).
     if (lane == 0) {
       constexpr int is_bf16 = __is_same(T, __nv_bfloat16) ? 1 : 0;
       constexpr uint32_t idesc_64 = ptx::make_idesc_f16(is_bf16, BM, BN, 0, 0);  // 128 x 64, both K-major
-      constexpr uint32_t idesc_pv = ptx::make_idesc_f16(is_bf16, BM, D, 0, 1);   // V is MN-major
       constexpr uint32_t mode = ptx::swizzle_mode_for_row_bytes(LO::kRowBytes);
       constexpr uint32_t sbo = 8 * LO::kRowBytes;
       constexpr int kSteps = LO::kRowBytes / 32;  // K=16 steps over d
@@ -715,9 +770,8 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       const uint32_t pk_lo = desc_lo(ptx::smem_u32(smem + LO::offPK), 16);
       const uint32_t fq_lo = desc_lo(ptx::smem_u32(smem + LO::offFQ), 16);
       const uint32_t k_lo = desc_lo(ptx::smem_u32(smem + LO::offK), 16);
-      const uint32_t v_lo = desc_lo(ptx::smem_u32(smem + LO::offV), (uint32_t)LO::kBlk);
-      uint32_t c_q = 0, c_front = 0, c_pv = 0, c_pk = 0, c_fq = 0, c_pt = 0;
-      uint32_t c_s0 = 0, c_s1 = 0, c_p0 = 0, c_p1 = 0;   // per stream: S tiles issued, PV issued
+      uint32_t c_q = 0, c_front = 0, c_pk = 0, c_fq = 0, c_pt = 0;
+      uint32_t c_s0 = 0, c_s1 = 0;   // per stream: S tiles issued
       bool ok = true;
 
       // D[128 x 64] = A[128 x d] * B[64 x d]^T, both operands K-major tiles in shared memory
@@ -729,34 +783,9 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
       };
 
-      // cursors over the CTA's (item, tile) sequence; items without a kept query row have no tiles
-      struct Cursor {
-        int k, it, u, n;
-        bool live;
-      };
-      Cursor cf{0, (int)blockIdx.x, 0, 0, false}, cp{0, (int)blockIdx.x, 0, 0, false};
-      // position the cursor on the first tile of the next item that has tiles; false when none is left or on abort
-      // Look at the item the cursor stands before: with tiles -> the cursor goes live on its first tile; without
-      // (no kept query row) -> the cursor steps over it.  Returns false on abort.
-      auto look = [&](Cursor& c, bool release) -> bool {
-        const int slot = c.k & 1;
-        if (!ptx::mbar_wait_inline(&bars->item_full[slot], (uint32_t)(c.k >> 1) & 1u, abort_flag, status_word, 31)) return false;
-        const ItemSlot* sl = &slots[slot];
-        if (sl->any_kept != 0) {
-          c.n = sl->t_end - sl->t_begin;
-          c.u = 0;
-          c.live = true;
-        } else {
-          if (release) ptx::mbar_arrive(&bars->item_empty[slot]);
-          ++c.k;
-          c.it += gridDim.x;
-        }
-        return true;
-      };
-
       // everything tile u needs before its softmax: new C2P block(s), PT, S
-      auto front = [&]() -> bool {
-        const int u = cf.u, n = cf.n, g = u & 1;
+      auto front = [&](int u, int n) -> bool {
+        const int g = u & 1;
         if (u == 0) {
           if (!ptx::mbar_wait_inline(&bars->q_full, c_q & 1u, abort_flag, status_word, 4)) return false;
           ++c_q;
@@ -823,81 +852,19 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         return true;
       };
 
-      auto pv = [&]() -> bool {
-        const int u = cp.u, g = u & 1;
-        const uint32_t c_p = g ? c_p1 : c_p0;
-        TRACE(30);
-        if (!ptx::mbar_wait_inline(&bars->p_full[g], c_p & 1u, abort_flag, status_word, 7)) return false;
-        TRACE(28);
-        const uint32_t vb = c_pv & 1u;
-        if (!ptx::mbar_wait_inline(&bars->v_full[vb], (c_pv >> 1) & 1u, abort_flag, status_word, 8)) return false;
-        TRACE(27);
-        ptx::tc_fence_after();
-        const uint32_t vt_lo = v_lo + vb * kBlkUnits;
-        const uint32_t d_tmem = tmem_base + COL_O + g * 64, a_tmem = tmem_base + COL_P + g * (BN / 2);
-        constexpr uint32_t kStepUnits = (16u * LO::kRowBytes) >> 4;   // 16 keys further down the V tile
-        if (u < 2) umma_ts_lohi<0>(d_tmem, a_tmem, vt_lo, desc_hi, idesc_pv);
-        else umma_ts_lohi<1>(d_tmem, a_tmem, vt_lo, desc_hi, idesc_pv);
-#pragma unroll
-        for (int kk = 1; kk < BN / 16; ++kk)
-          umma_ts_lohi<1>(d_tmem, a_tmem + kk * 8, vt_lo + kk * kStepUnits, desc_hi, idesc_pv);
-        ptx::umma_commit(&bars->v_empty[vb]);
-        ptx::umma_commit(&bars->o_ready[g]);
-        if (g) ++c_p1; else ++c_p0;
-        ++c_pv;
-        TRACE(31);
-        return true;
-      };
-
-      // The front cursor may be at most one item past the PV cursor: item slots are double-buffered, and the slot of
-      // item k+2 is published only after this thread has released item k (which the PV cursor does).
-      int ahead = 0;            // fronts issued whose PV is still to come
-      while (ok) {
-        if (!cp.live && cp.it < n_items) {   // the trailing cursor may always wait for its item
-          ok = look(cp, true);
-          if (cf.k < cp.k) {   // it stepped over an item without tiles that the front cursor had not looked at yet
-            cf.k = cp.k;
-            cf.it = cp.it;
-          }
-          continue;
+      // The fronts run ahead of the softmax streams as far as the buffers allow, also into the next item; the PV of
+      // a tile is issued by the softmax stream that produced its P.
+      int k = 0;
+      for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++k) {
+        const int slot = k & 1;
+        ok = ptx::mbar_wait_inline(&bars->item_full[slot], (uint32_t)(k >> 1) & 1u, abort_flag, status_word, 31);
+        if (!ok) break;
+        const ItemSlot* sl = &slots[slot];
+        if (sl->any_kept != 0) {
+          const int n = sl->t_end - sl->t_begin;
+          for (int u = 0; u < n && ok; ++u) ok = front(u, n);
         }
-        if (!cf.live && cf.it < n_items && cf.k <= cp.k + 1) {
-          // never block on the next item's slot while a PV can still be issued: the loader reaches that item only
-          // after the buffers those PVs release
-          const bool pv_pending = cp.live && ahead >= 1;
-          if (!pv_pending || ptx::mbar_try_wait(&bars->item_full[cf.k & 1], (uint32_t)(cf.k >> 1) & 1u)) {
-            ok = look(cf, false);
-            continue;
-          }
-        }
-        if (!cf.live && !cp.live) break;
-        // A PV whose P tile is already waiting goes first (the softmax stream needs its completion two tiles on);
-        // otherwise prepare tiles up to three ahead, and only then block on the oldest PV.
-        bool do_pv = cp.live && (ahead >= 3 || !cf.live);
-        if (!do_pv && cp.live && ahead >= 1) {
-          const int g = cp.u & 1;
-          do_pv = ptx::mbar_try_wait(&bars->p_full[g], (g ? c_p1 : c_p0) & 1u);
-        }
-        if (do_pv) {
-          ok = pv();
-          if (!ok) break;
-          --ahead;
-          if (++cp.u == cp.n) {
-            ptx::mbar_arrive(&bars->item_empty[cp.k & 1]);
-            ++cp.k;
-            cp.it += gridDim.x;
-            cp.live = false;
-          }
-        } else {
-          ok = front();
-          if (!ok) break;
-          ++ahead;
-          if (++cf.u == cf.n) {
-            ++cf.k;
-            cf.it += gridDim.x;
-            cf.live = false;
-          }
-        }
+        ptx::mbar_arrive(&bars->item_empty[slot]);
       }
     }
     }

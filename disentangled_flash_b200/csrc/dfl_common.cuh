@@ -98,8 +98,6 @@ int launch_gemm_tc(const GemmDesc& g, cudaStream_t stream);
 
 int launch_attention_simt(const DflAttnParams& p, cudaStream_t stream);
 int launch_attention_tc(const DflAttnParams& p, cudaStream_t stream);
-bool attention_fused_supported(const DflAttnTablesParams& p);
-int launch_attention_fused(const DflAttnTablesParams& p, cudaStream_t stream);
 bool attention_rel_supported(const DflAttnRelParams& p);
 int launch_attention_rel(const DflAttnRelParams& p, cudaStream_t stream);
 int launch_expand_rel_tables(const void* pos, const int32_t* lut, void* rel, int heads, int n_active, int seq_len,

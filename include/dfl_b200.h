@@ -196,18 +196,6 @@ typedef struct DflAttnTablesParams {
 DFL_API int    dfl_attention_fwd_static(const DflAttnTablesParams* p, void* stream);
 DFL_API size_t dfl_static_scratch_bytes(void);
 
-/*
- * Fused attention that takes the pruned position tables instead of precomputed score tensors
- * (DflAttnTablesParams above): the C2P/P2C scores are produced inside the kernel by tcgen05 from
- * pos_key / pos_query [H,A,d], rounded to the input type like the separate score GEMMs do, and
- * consumed from shared memory, so the two [B,H,L,A] tensors are never written to or read from
- * global memory.  Replaces, in one launch, the two torch.matmul calls (kernel.py:574-585) and the
- * Triton kernel (kernel.py:137-429).  Covered: FP16/BF16, head_dim 32 or 64, at least one position
- * term, n_active <= 4096, seq_len <= 1024; dfl_attention_tables_supported() tells, and other
- * configurations return DFL_ERR_UNSUPPORTED (use dfl_pos_scores + dfl_attention_fwd for them).
- */
-DFL_API int dfl_attention_tables_supported(const DflAttnTablesParams* p);
-DFL_API int dfl_attention_tables_fwd(const DflAttnTablesParams* p, void* stream);
 
 /*
  * Fused attention over position tables laid out by relative distance.

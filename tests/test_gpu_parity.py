@@ -231,58 +231,6 @@ def test_padded_query_rows_are_uniform_and_runs_are_deterministic(dtype_name, al
     assert_close(a.cpu()[padded], mean_v[padded], dtype, "padded rows = mean(V)")
 
 
-# ------------------------------------------------------------------ scores computed in-kernel
-def run_tables(case, status=None):
-    c = _cabi()
-    to = lambda t: None if t is None else t.to(dev)  # noqa: E731
-    status = torch.zeros(1, dtype=torch.int32, device=dev) if status is None else status
-    out = c.attention_tables_fwd(to(case["q"]), to(case["k"]), to(case["v"]), to(case["pos_key"]),
-                                 to(case["pos_query"]), to(case["lut"]), to(case["mask"]), case["scale"], status=status)
-    assert status.item() == 0, f"a bounded device-side wait expired (code {status.item()})"
-    return out
-
-
-@pytest.mark.parametrize("dtype_name", ("fp16", "bf16"))
-@pytest.mark.parametrize("d", (32, 64))
-def test_tables_kernel_lengths(dtype_name, d):
-    dtype = DTYPES[dtype_name]
-    status = torch.zeros(1, dtype=torch.int32, device=dev)
-    for length in CORE_LENGTHS + (1024,):
-        case = make_core_case(2, 2, length, d, dtype, seed=2000 + length, mask="right")
-        assert _cabi().attention_tables_supported(case["q"].to(dev), case["pos_key"].to(dev), case["pos_query"].to(dev))
-        got = run_tables(case, status)
-        assert status.item() == 0, f"device wait expired, code {status.item()} at L={length}"
-        assert_close(got, oracle_core(case), dtype, f"tables kernel L={length} d={d} {dtype_name}")
-        # same arithmetic as the two-call path (score GEMM rounding included): results agree to rounding of P
-        two = run_core(case, "auto")
-        assert_close(got, two.float().cpu(), dtype, f"tables vs two-call L={length}")
-
-
-@pytest.mark.parametrize("dtype_name", ("fp16", "bf16"))
-@pytest.mark.parametrize("mask", MASK_PATTERNS)
-@pytest.mark.parametrize("mode", ("both", "c2p", "p2c"))
-def test_tables_kernel_masks_and_modes(dtype_name, mask, mode):
-    dtype = DTYPES[dtype_name]
-    for length, d, buckets, max_pos in ((65, 64, 256, 512), (200, 32, 256, 512), (300, 64, 32, 64), (700, 64, 256, 512)):
-        case = make_core_case(2, 2, length, d, dtype, seed=17 + length, mask=mask, mode=mode, buckets=buckets,
-                              max_pos=max_pos)
-        got = run_tables(case)
-        assert_close(got, oracle_core(case), dtype, f"tables kernel mask={mask} mode={mode} L={length}")
-
-
-def test_tables_kernel_is_deterministic_and_reports_unsupported():
-    case = make_core_case(3, 4, 384, 64, torch.float16, seed=5, mask="all")
-    a, b = run_tables(case), run_tables(case)
-    assert torch.equal(a, b)
-    c = _cabi()
-    big = make_core_case(1, 1, 64, 128, torch.float16, seed=6)
-    assert not c.attention_tables_supported(big["q"].to(dev), big["pos_key"].to(dev), big["pos_query"].to(dev))
-    with pytest.raises(c.DflError, match="not covered"):
-        run_tables(big)
-    f32 = make_core_case(1, 1, 64, 64, torch.float32, seed=7)
-    assert not c.attention_tables_supported(f32["q"].to(dev), f32["pos_key"].to(dev), f32["pos_query"].to(dev))
-
-
 # ------------------------------------------------------------------ module level (golden fixtures)
 def build_module(g, dtype):
     import disentangled_flash_b200 as df
