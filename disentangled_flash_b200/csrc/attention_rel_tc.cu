@@ -140,25 +140,13 @@ __device__ __forceinline__ void umma_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, u
       : "memory");
 }
 
-// 16-bit shared-memory load at base + compile-time byte offset.
-template <int OFF>
-__device__ __forceinline__ uint16_t lds_u16_off(uint32_t saddr) {
-  uint16_t v;
-  asm volatile("ld.shared.u16 %0, [%1+%2];" : "=h"(v) : "r"(saddr), "n"(OFF) : "memory");
+// 16-bit shared-memory load, zero-extended into a 32-bit register (32-bit destinations keep every value in its
+// own register; the address arithmetic of unrolled callers folds into the instruction's immediate offset).
+__device__ __forceinline__ uint32_t lds_u16_r32(uint32_t saddr) {
+  uint32_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(saddr) : "memory");
   return v;
 }
-
-template <typename T, int X, int N, int STRIDE>
-struct GatherAdd {
-  static __device__ __forceinline__ void run(float* s, uint32_t saddr) {
-    s[X] = Pack2<T>::add(s[X], lds_u16_off<X * STRIDE>(saddr));
-    GatherAdd<T, X + 1, N, STRIDE>::run(s, saddr);
-  }
-};
-template <typename T, int N, int STRIDE>
-struct GatherAdd<T, N, N, STRIDE> {
-  static __device__ __forceinline__ void run(float*, uint32_t) {}
-};
 
 // Kept-key bits of batch row b: lane w returns word w (keys [32w, 32w+32)) built from its own 32 mask elements.
 __device__ __forceinline__ uint32_t kept_bits_word(const DflAttnRelParams& p, int b, int lane) {
@@ -295,19 +283,21 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     bool ok = true;
 
     // 64 fp32 columns at t_src -> 64 16-bit values at dst (4-byte aligned), rounded like a GEMM epilogue
+    // (both halves are in flight before the single wait: a TMEM round trip costs several hundred cycles)
     auto convert_64 = [&](uint32_t t_src, unsigned char* dst, bool mirror) {
+      uint32_t raw0[32], raw1[32];
+      ptx::tmem_ld32(t_src, raw0);
+      ptx::tmem_ld32(t_src + 32, raw1);
+      ptx::tmem_wait_ld();
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t raw[32];
-        ptx::tmem_ld32(t_src + half * 32, raw);
-        ptx::tmem_wait_ld();
-#pragma unroll
-        for (int x = 0; x < 32; x += 2) {
-          const uint32_t w = Pack2<T>::pack(__uint_as_float(raw[x]), __uint_as_float(raw[x + 1]));
-          *reinterpret_cast<uint32_t*>(dst + half * 64 + x * 2) = w;
-          if (half == 0 && x < RING_MIRROR && mirror) *reinterpret_cast<uint32_t*>(dst + RING_COLS * 2 + x * 2) = w;
-        }
+      for (int x = 0; x < 32; x += 2) {
+        const uint32_t w = Pack2<T>::pack(__uint_as_float(raw0[x]), __uint_as_float(raw0[x + 1]));
+        *reinterpret_cast<uint32_t*>(dst + x * 2) = w;
+        if (x < RING_MIRROR && mirror) *reinterpret_cast<uint32_t*>(dst + RING_COLS * 2 + x * 2) = w;
       }
+#pragma unroll
+      for (int x = 0; x < 32; x += 2)
+        *reinterpret_cast<uint32_t*>(dst + 64 + x * 2) = Pack2<T>::pack(__uint_as_float(raw1[x]), __uint_as_float(raw1[x + 1]));
     };
 
     int k = 0;
@@ -490,111 +480,164 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 
         for (int u = g; u < n && ok; u += 2) {
           const int t = t_begin + u, j0 = t * BN;
-          ok = ptx::mbar_wait_inline(&bars->s_full[g], c_t & 1u, abort_flag, status_word, 9);
+          // The stream's previous PV must be complete before its P operand is overwritten or O is rescaled.
+          ok = ptx::mbar_wait_inline(&bars->o_ready[g], (c_t & 1u) ^ 1u, abort_flag, status_word, 22) &&
+               ptx::mbar_wait_inline(&bars->s_full[g], c_t & 1u, abort_flag, status_word, 9);
+          if (ok && has_c2p) ok = ptx::mbar_wait_inline(&bars->c2p_ready[g], c_t & 1u, abort_flag, status_word, 10);
+          if (ok && has_p2c) ok = ptx::mbar_wait_inline(&bars->pt_ready[g], c_t & 1u, abort_flag, status_word, 21);
           if (!ok) break;
           TRACE(1);
           ptx::tc_fence_after();
-          float s[BN];
-          {
-            uint32_t raw0[32], raw1[32];
-            ptx::tmem_ld32(t_s, raw0);
-            ptx::tmem_ld32(t_s + 32, raw1);
-            ptx::tmem_wait_ld();
-#pragma unroll
-            for (int x = 0; x < 32; ++x) {
-              s[x] = __uint_as_float(raw0[x]);
-              s[32 + x] = __uint_as_float(raw1[x]);
-            }
-          }
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(&bars->s_free[g]);
-          TRACE(2);
-
-          if (has_c2p) {
-            ok = ptx::mbar_wait_inline(&bars->c2p_ready[g], c_t & 1u, abort_flag, status_word, 10);
-            if (!ok) break;
-            // ring column of (row r, key n of the tile): (64 * block index of the tile + 128 - r + n) mod 256
-            const uint32_t cb = (64u * (c_blk0 + (uint32_t)u) + 128u - (uint32_t)r) & 255u;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint32_t base = (cb + 16u * q) & 255u;   // a 16-key run stays inside columns [base, base+16) <= 271
-              GatherAdd<T, 0, 16, 2>::run(s + 16 * q, ring_addr + 2u * base);
-            }
-          }
-          if (has_p2c) {
-            ok = ptx::mbar_wait_inline(&bars->pt_ready[g], c_t & 1u, abort_flag, status_word, 21);
-            if (!ok) break;
-            GatherAdd<T, 0, BN, (PT_PITCH_H + 1) * 2>::run(s, pt_addr);
-          }
-          __syncwarp();
-          if (lane == 0) {
-            if (has_c2p) ptx::mbar_arrive(&bars->ring_release[g]);
-            if (has_p2c) ptx::mbar_arrive(&bars->pt_release[g]);
-          }
-          TRACE(3);
-
-          // ---- mask: keys >= L and padded keys -> -inf; a padded query row -> 0 on every in-range key
+          // ring column of (row r, key x of the tile): (64 * block index of the tile + 128 - r + x) mod 256
+          const uint32_t cb = (64u * (c_blk0 + (uint32_t)u) + 128u - (uint32_t)r) & 255u;
           const uint32_t kb0 = sl->kbits[2 * t], kb1 = sl->kbits[2 * t + 1];
+          const bool keys_all_kept = (kb0 & kb1) == 0xffffffffu;
           const int n_in = L - j0;
-          if (!q_keep) {
-#pragma unroll
-            for (int x = 0; x < BN; ++x) s[x] = x < n_in ? 0.0f : -INFINITY;
-          } else if ((kb0 & kb1) != 0xffffffffu) {
-#pragma unroll
-            for (int x = 0; x < BN; ++x) {
-              const uint32_t w = x < 32 ? kb0 : kb1;
-              if (!((w >> (x & 31)) & 1u)) s[x] = -INFINITY;
-            }
-          }
-          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-          for (int x = 0; x < BN; ++x) mx[x & 3] = fmaxf(mx[x & 3], s[x]);
-          const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-          // Lazy reference maximum: m_run only moves when the tile maximum exceeds it by more than 2^8 after
-          // scaling, so exp2 arguments stay <= 8 (P <= 256, exact range of both 16-bit types) and the O accumulator
-          // in TMEM needs rescaling only on those rare tiles.
-          const bool move = tile_max > m_run + attn::kLazyMaxSlack / cscale;  // also true for the first finite maximum
-          const float m_new = move ? tile_max : m_run;
-          const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-          const float corr = move ? ptx::ex2_approx((m_run - m_use) * cscale) : 1.0f;
-          const float neg_m = -m_use * cscale;
-          float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-          uint32_t packed[BN / 2];
-#pragma unroll
-          for (int x = 0; x < BN; x += 2) {
-            const float p0 = ptx::ex2_approx(fmaf(s[x], cscale, neg_m));
-            const float p1 = ptx::ex2_approx(fmaf(s[x + 1], cscale, neg_m));
-            sum[(x >> 1) & 3] += p0 + p1;
-            packed[x / 2] = Pack2<T>::pack(p0, p1);
-          }
-          l_run = l_run * corr + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
-          m_run = m_new;
-          TRACE(4);
 
-          // The stream's previous PV must be complete before its P operand is overwritten or O is rescaled.
-          ok = ptx::mbar_wait_inline(&bars->o_ready[g], (c_t & 1u) ^ 1u, abort_flag, status_word, 22);
-          if (!ok) break;
-          if (u >= 2 && __any_sync(0xffffffffu, corr != 1.0f)) {
-            ptx::tc_fence_after();
-#pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
-              uint32_t o[32];
-              ptx::tmem_ld32(t_o + c0, o);
+          // The tile is walked in four chunks of 16 keys by one rolled loop (a small loop body stays in the
+          // instruction cache; a fully unrolled 64-key body does not): S chunk from TMEM, the two relative terms
+          // from shared memory, mask, exp2 against the running reference maximum, P chunk to TMEM.
+          // Lazy reference maximum: m_run moves only when a chunk maximum exceeds it by more than 2^8 after scaling,
+          // so exp2 arguments stay <= 8 (P <= 256, exact range of both 16-bit types) and O needs rescaling rarely.
+          // A move is simple at the tile's first chunk.  At a later chunk the P chunks already written would be
+          // stale: the rest of the tile is then only scanned for its maximum (pass 1), the reference is moved, and
+          // the tile is walked again (pass 2; S, the ring and the PT tile are released only after the last pass).
+          int pass = 0;
+          float tile_max = -INFINITY;
+          for (;;) {
+            float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            // One TMEM round trip per pass (a tcgen05.ld -> wait::ld pair costs several hundred cycles, and wait::ld
+            // drains every outstanding load, so per-chunk loads cannot be pipelined): the whole S row is fetched at
+            // once and the rolled loop consumes the first 16 registers, then rotates the rest down.
+            uint32_t raw[BN];
+            {
+              uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[0]);
+              uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[32]);
+              ptx::tmem_ld32(t_s, lo);
+              ptx::tmem_ld32(t_s + 32, hi);
               ptx::tmem_wait_ld();
+            }
+#pragma unroll 1
+            for (int q = 0; q < 4; ++q) {
+              float s[16];
 #pragma unroll
-              for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * corr);
-              ptx::tmem_st32(t_o + c0, o);
+              for (int x = 0; x < 16; ++x) s[x] = __uint_as_float(raw[x]);
+#pragma unroll
+              for (int x = 0; x < BN - 16; ++x) raw[x] = raw[x + 16];
+              // per term: 16 loads issued before the 16 adds that use them (a warp issues in order; a load followed
+              // at once by its consumer would expose the shared-memory latency once per element)
+              if (has_c2p) {
+                const uint32_t base = (cb + 16u * q) & 255u;   // a 16-key run stays inside columns [base, base+16) <= 271
+                const uint32_t caddr = ring_addr + 2u * base;
+                uint32_t cv[16];
+#pragma unroll
+                for (int x = 0; x < 16; ++x) cv[x] = lds_u16_r32(caddr + 2u * x);
+#pragma unroll
+                for (int x = 0; x < 16; ++x) s[x] = Pack2<T>::add(s[x], (uint16_t)cv[x]);
+              }
+              if (has_p2c) {
+                const uint32_t paddr = pt_addr + (uint32_t)(q * 16 * (PT_PITCH_H + 1) * 2);
+                uint32_t pv[16];
+#pragma unroll
+                for (int x = 0; x < 16; ++x) pv[x] = lds_u16_r32(paddr + (uint32_t)(x * (PT_PITCH_H + 1) * 2));
+#pragma unroll
+                for (int x = 0; x < 16; ++x) s[x] = Pack2<T>::add(s[x], (uint16_t)pv[x]);
+              }
+              // mask: keys >= L and padded keys -> -inf; a padded query row -> 0 on every in-range key
+              if (!q_keep) {
+#pragma unroll
+                for (int x = 0; x < 16; ++x) s[x] = 16 * q + x < n_in ? 0.0f : -INFINITY;
+              } else if (!keys_all_kept) {
+                const uint32_t kbq = ((q < 2 ? kb0 : kb1) >> ((q & 1) * 16)) & 0xffffu;
+#pragma unroll
+                for (int x = 0; x < 16; ++x)
+                  if (!((kbq >> x) & 1u)) s[x] = -INFINITY;
+              }
+              float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+              for (int x = 0; x < 16; ++x) mx[x & 3] = fmaxf(mx[x & 3], s[x]);
+              const float cmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+              tile_max = fmaxf(tile_max, cmax);
+              if (pass == 1) continue;   // scanning for the maximum only
+              if (pass == 0) {
+                const bool move = cmax > m_run + attn::kLazyMaxSlack / cscale;  // also true for the first finite maximum
+                if (__any_sync(0xffffffffu, move)) {
+                  if (q != 0) {
+                    pass = 1;
+                    continue;
+                  }
+                  const float m_new = move ? cmax : m_run;
+                  const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+                  const float corr = move ? ptx::ex2_approx((m_run - m_use) * cscale) : 1.0f;   // 0 when m_run = -inf
+                  m_run = m_new;
+                  l_run *= corr;
+                  if (u >= 2) {   // the stream already accumulated into O in this item
+#pragma unroll 1
+                    for (int c0 = 0; c0 < D; c0 += 8) {   // rare: small rolled steps keep the register footprint low
+                      uint32_t o[8];
+                      ptx::tmem_ld8(t_o + c0, o);
+                      ptx::tmem_wait_ld();
+#pragma unroll
+                      for (int x = 0; x < 8; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * corr);
+                      ptx::tmem_st8(t_o + c0, o);
+                    }
+                  }
+                }
+              }
+              const float neg_m = -(m_run == -INFINITY ? 0.0f : m_run) * cscale;
+              uint32_t packed[8];
+              // staged by kind of instruction (arguments, exp2, sums and packing): a warp issues in order
+#pragma unroll
+              for (int x = 0; x < 16; ++x) s[x] = fmaf(s[x], cscale, neg_m);
+#pragma unroll
+              for (int x = 0; x < 16; ++x) s[x] = ptx::ex2_approx(s[x]);
+#pragma unroll
+              for (int x = 0; x < 16; x += 2) packed[x / 2] = Pack2<T>::pack(s[x], s[x + 1]);
+              // The row sum is taken over P as rounded for the tensor core, so that the weights P/l the output is
+              // built from sum to one exactly.  (The reference sums the unrounded values, kernel.py:316-333; with the
+              // lazy reference maximum the largest P of a row is not the exactly representable 1.0, and an unrounded
+              // sum would leave the rounding error of the dominant key uncompensated.)
+#pragma unroll
+              for (int x = 0; x < 8; ++x) sum[x & 3] += Pack2<T>::sum2(packed[x]);
+              ptx::tmem_st8(t_p + 8 * q, packed);
+            }
+            if (pass == 0 || pass == 2) {
+              l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+              break;
+            }
+            // pass 1 done: tile_max is the row's maximum over the whole tile.  Move the reference where needed,
+            // drop this tile's partial sums, and walk the tile again.
+            {
+              const bool move = tile_max > m_run + attn::kLazyMaxSlack / cscale;
+              const float m_new = move ? tile_max : m_run;
+              const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+              const float corr = move ? ptx::ex2_approx((m_run - m_use) * cscale) : 1.0f;
+              m_run = m_new;
+              l_run *= corr;   // this tile's sums are only added after its final pass
+              if (u >= 2 && __any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 8) {
+                  uint32_t o[8];
+                  ptx::tmem_ld8(t_o + c0, o);
+                  ptx::tmem_wait_ld();
+#pragma unroll
+                  for (int x = 0; x < 8; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * corr);
+                  ptx::tmem_st8(t_o + c0, o);
+                }
+              }
+              pass = 2;
             }
           }
-          {
-            uint32_t (&pk)[32] = *reinterpret_cast<uint32_t (*)[32]>(&packed[0]);
-            ptx::tmem_st32(t_p, pk);
-          }
+          TRACE(4);
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(&bars->p_full[g]);
+          if (lane == 0) {
+            ptx::mbar_arrive(&bars->s_free[g]);
+            if (has_c2p) ptx::mbar_arrive(&bars->ring_release[g]);
+            if (has_p2c) ptx::mbar_arrive(&bars->pt_release[g]);
+            ptx::mbar_arrive(&bars->p_full[g]);
+          }
           ++c_t;
           TRACE(5);
         }

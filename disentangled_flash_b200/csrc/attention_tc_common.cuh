@@ -43,6 +43,11 @@ struct Pack2<__half> {
     asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"(x), "f"(acc));
     return d;
   }
+  // sum of the two packed values, exactly as the tensor core will read them
+  static __device__ __forceinline__ float sum2(uint32_t w) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    return f.x + f.y;
+  }
 };
 template <>
 struct Pack2<__nv_bfloat16> {
@@ -54,6 +59,9 @@ struct Pack2<__nv_bfloat16> {
     float d;
     asm("add.rn.f32.bf16 %0, %1, %2;" : "=f"(d) : "h"(x), "f"(acc));
     return d;
+  }
+  static __device__ __forceinline__ float sum2(uint32_t w) {
+    return __uint_as_float(w << 16) + __uint_as_float(w & 0xffff0000u);
   }
 };
 

@@ -14,7 +14,7 @@ including items without any kept query row.
 import pytest
 import torch
 
-from helpers import MASK_PATTERNS, assert_close, make_core_case, oracle_core
+from helpers import MASK_PATTERNS, assert_close, make_core_case, oracle_core, tolerance
 
 pytestmark = pytest.mark.gpu
 
@@ -83,8 +83,11 @@ def test_rel_kernel_lengths(dtype_name, d):
         assert _cabi().attention_rel_supported(dtype, length, d, True, True)
         got = run_rel(case, status)
         assert_close(got, oracle_core(case), dtype, f"rel kernel L={length} d={d} {dtype_name}")
-        # same arithmetic as the two-call path (score rounding included): results agree to the rounding of P
-        assert_close(got, run_two_call(case).float().cpu(), dtype, f"rel vs two-call L={length}")
+        # Same arithmetic as the two-call path up to the softmax reference maximum (which changes how P rounds):
+        # two results that each meet the bound against the oracle can differ by twice the bound.
+        two = run_two_call(case).float().cpu()
+        err = (got.float().cpu() - two).abs().double()
+        assert (err <= 2 * tolerance(dtype, two)).all(), f"rel vs two-call L={length}: {err.max().item():.3e}"
 
 
 @pytest.mark.parametrize("dtype_name", sorted(DTYPES))
