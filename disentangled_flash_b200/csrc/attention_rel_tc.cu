@@ -495,128 +495,80 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           const int n_in = L - j0;
 
           // The tile is walked in four chunks of 16 keys by one rolled loop (a small loop body stays in the
-          // instruction cache; a fully unrolled 64-key body does not): S chunk from TMEM, the two relative terms
-          // from shared memory, mask, exp2 against the running reference maximum, P chunk to TMEM.
+          // instruction cache; a fully unrolled 64-key body does not): the two relative terms from shared memory,
+          // mask, exp2 against the running reference maximum, P chunk to TMEM.
+          // One TMEM round trip per tile (a tcgen05.ld -> wait::ld pair costs several hundred cycles, and wait::ld
+          // drains every outstanding load, so per-chunk loads cannot be pipelined): the whole S row is fetched at
+          // once - which also frees the S buffer for the MMA of the stream's next tile right away - and the loop
+          // consumes the first 16 registers, then rotates the rest down.
+          uint32_t raw[BN];
+          {
+            uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[0]);
+            uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[32]);
+            ptx::tmem_ld32(t_s, lo);
+            ptx::tmem_ld32(t_s + 32, hi);
+            ptx::tmem_wait_ld();
+          }
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&bars->s_free[g]);
+          TRACE(2);
+
           // Lazy reference maximum: m_run moves only when a chunk maximum exceeds it by more than 2^8 after scaling,
           // so exp2 arguments stay <= 8 (P <= 256, exact range of both 16-bit types) and O needs rescaling rarely.
-          // A move is simple at the tile's first chunk.  At a later chunk the P chunks already written would be
-          // stale: the rest of the tile is then only scanned for its maximum (pass 1), the reference is moved, and
-          // the tile is walked again (pass 2; S, the ring and the PT tile are released only after the last pass).
-          int pass = 0;
-          float tile_max = -INFINITY;
-          for (;;) {
-            float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            // One TMEM round trip per pass (a tcgen05.ld -> wait::ld pair costs several hundred cycles, and wait::ld
-            // drains every outstanding load, so per-chunk loads cannot be pipelined): the whole S row is fetched at
-            // once and the rolled loop consumes the first 16 registers, then rotates the rest down.
-            uint32_t raw[BN];
-            {
-              uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[0]);
-              uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[32]);
-              ptx::tmem_ld32(t_s, lo);
-              ptx::tmem_ld32(t_s + 32, hi);
-              ptx::tmem_wait_ld();
-            }
+          // On a move, everything accumulated against the old reference is rescaled: the row sum, O in TMEM (if the
+          // stream already accumulated in this item) and the P chunks of this tile that are already written.
+          float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 1
-            for (int q = 0; q < 4; ++q) {
-              float s[16];
+          for (int q = 0; q < 4; ++q) {
+            float s[16];
 #pragma unroll
-              for (int x = 0; x < 16; ++x) s[x] = __uint_as_float(raw[x]);
+            for (int x = 0; x < 16; ++x) s[x] = __uint_as_float(raw[x]);
 #pragma unroll
-              for (int x = 0; x < BN - 16; ++x) raw[x] = raw[x + 16];
-              // per term: 16 loads issued before the 16 adds that use them (a warp issues in order; a load followed
-              // at once by its consumer would expose the shared-memory latency once per element)
-              if (has_c2p) {
-                const uint32_t base = (cb + 16u * q) & 255u;   // a 16-key run stays inside columns [base, base+16) <= 271
-                const uint32_t caddr = ring_addr + 2u * base;
-                uint32_t cv[16];
+            for (int x = 0; x < BN - 16; ++x) raw[x] = raw[x + 16];
+            // per term: 16 loads issued before the 16 adds that use them (a warp issues in order; a load followed
+            // at once by its consumer would expose the shared-memory latency once per element)
+            if (has_c2p) {
+              const uint32_t base = (cb + 16u * q) & 255u;   // a 16-key run stays inside columns [base, base+16) <= 271
+              const uint32_t caddr = ring_addr + 2u * base;
+              uint32_t cv[16];
 #pragma unroll
-                for (int x = 0; x < 16; ++x) cv[x] = lds_u16_r32(caddr + 2u * x);
+              for (int x = 0; x < 16; ++x) cv[x] = lds_u16_r32(caddr + 2u * x);
 #pragma unroll
-                for (int x = 0; x < 16; ++x) s[x] = Pack2<T>::add(s[x], (uint16_t)cv[x]);
-              }
-              if (has_p2c) {
-                const uint32_t paddr = pt_addr + (uint32_t)(q * 16 * (PT_PITCH_H + 1) * 2);
-                uint32_t pv[16];
-#pragma unroll
-                for (int x = 0; x < 16; ++x) pv[x] = lds_u16_r32(paddr + (uint32_t)(x * (PT_PITCH_H + 1) * 2));
-#pragma unroll
-                for (int x = 0; x < 16; ++x) s[x] = Pack2<T>::add(s[x], (uint16_t)pv[x]);
-              }
-              // mask: keys >= L and padded keys -> -inf; a padded query row -> 0 on every in-range key
-              if (!q_keep) {
-#pragma unroll
-                for (int x = 0; x < 16; ++x) s[x] = 16 * q + x < n_in ? 0.0f : -INFINITY;
-              } else if (!keys_all_kept) {
-                const uint32_t kbq = ((q < 2 ? kb0 : kb1) >> ((q & 1) * 16)) & 0xffffu;
-#pragma unroll
-                for (int x = 0; x < 16; ++x)
-                  if (!((kbq >> x) & 1u)) s[x] = -INFINITY;
-              }
-              float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-              for (int x = 0; x < 16; ++x) mx[x & 3] = fmaxf(mx[x & 3], s[x]);
-              const float cmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-              tile_max = fmaxf(tile_max, cmax);
-              if (pass == 1) continue;   // scanning for the maximum only
-              if (pass == 0) {
-                const bool move = cmax > m_run + attn::kLazyMaxSlack / cscale;  // also true for the first finite maximum
-                if (__any_sync(0xffffffffu, move)) {
-                  if (q != 0) {
-                    pass = 1;
-                    continue;
-                  }
-                  const float m_new = move ? cmax : m_run;
-                  const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-                  const float corr = move ? ptx::ex2_approx((m_run - m_use) * cscale) : 1.0f;   // 0 when m_run = -inf
-                  m_run = m_new;
-                  l_run *= corr;
-                  if (u >= 2) {   // the stream already accumulated into O in this item
-#pragma unroll 1
-                    for (int c0 = 0; c0 < D; c0 += 8) {   // rare: small rolled steps keep the register footprint low
-                      uint32_t o[8];
-                      ptx::tmem_ld8(t_o + c0, o);
-                      ptx::tmem_wait_ld();
-#pragma unroll
-                      for (int x = 0; x < 8; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * corr);
-                      ptx::tmem_st8(t_o + c0, o);
-                    }
-                  }
-                }
-              }
-              const float neg_m = -(m_run == -INFINITY ? 0.0f : m_run) * cscale;
-              uint32_t packed[8];
-              // staged by kind of instruction (arguments, exp2, sums and packing): a warp issues in order
-#pragma unroll
-              for (int x = 0; x < 16; ++x) s[x] = fmaf(s[x], cscale, neg_m);
-#pragma unroll
-              for (int x = 0; x < 16; ++x) s[x] = ptx::ex2_approx(s[x]);
-#pragma unroll
-              for (int x = 0; x < 16; x += 2) packed[x / 2] = Pack2<T>::pack(s[x], s[x + 1]);
-              // The row sum is taken over P as rounded for the tensor core, so that the weights P/l the output is
-              // built from sum to one exactly.  (The reference sums the unrounded values, kernel.py:316-333; with the
-              // lazy reference maximum the largest P of a row is not the exactly representable 1.0, and an unrounded
-              // sum would leave the rounding error of the dominant key uncompensated.)
-#pragma unroll
-              for (int x = 0; x < 8; ++x) sum[x & 3] += Pack2<T>::sum2(packed[x]);
-              ptx::tmem_st8(t_p + 8 * q, packed);
+              for (int x = 0; x < 16; ++x) s[x] = Pack2<T>::add(s[x], (uint16_t)cv[x]);
             }
-            if (pass == 0 || pass == 2) {
-              l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-              break;
+            if (has_p2c) {
+              const uint32_t paddr = pt_addr + (uint32_t)(q * 16 * (PT_PITCH_H + 1) * 2);
+              uint32_t pv[16];
+#pragma unroll
+              for (int x = 0; x < 16; ++x) pv[x] = lds_u16_r32(paddr + (uint32_t)(x * (PT_PITCH_H + 1) * 2));
+#pragma unroll
+              for (int x = 0; x < 16; ++x) s[x] = Pack2<T>::add(s[x], (uint16_t)pv[x]);
             }
-            // pass 1 done: tile_max is the row's maximum over the whole tile.  Move the reference where needed,
-            // drop this tile's partial sums, and walk the tile again.
-            {
-              const bool move = tile_max > m_run + attn::kLazyMaxSlack / cscale;
-              const float m_new = move ? tile_max : m_run;
+            // mask: keys >= L and padded keys -> -inf; a padded query row -> 0 on every in-range key
+            if (!q_keep) {
+#pragma unroll
+              for (int x = 0; x < 16; ++x) s[x] = 16 * q + x < n_in ? 0.0f : -INFINITY;
+            } else if (!keys_all_kept) {
+              const uint32_t kbq = ((q < 2 ? kb0 : kb1) >> ((q & 1) * 16)) & 0xffffu;
+#pragma unroll
+              for (int x = 0; x < 16; ++x)
+                if (!((kbq >> x) & 1u)) s[x] = -INFINITY;
+            }
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int x = 0; x < 16; ++x) mx[x & 3] = fmaxf(mx[x & 3], s[x]);
+            const float cmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            const bool move = cmax > m_run + attn::kLazyMaxSlack / cscale;  // also true for the first finite maximum
+            if (__any_sync(0xffffffffu, move)) {
+              const float m_new = move ? cmax : m_run;
               const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-              const float corr = move ? ptx::ex2_approx((m_run - m_use) * cscale) : 1.0f;
+              const float corr = move ? ptx::ex2_approx((m_run - m_use) * cscale) : 1.0f;   // 0 when m_run = -inf
               m_run = m_new;
-              l_run *= corr;   // this tile's sums are only added after its final pass
-              if (u >= 2 && __any_sync(0xffffffffu, corr != 1.0f)) {
+              l_run *= corr;
+              if (u >= 2) {   // the stream already accumulated into O in this item
 #pragma unroll 1
-                for (int c0 = 0; c0 < D; c0 += 8) {
+                for (int c0 = 0; c0 < D; c0 += 8) {   // rare: small rolled steps keep the register footprint low
                   uint32_t o[8];
                   ptx::tmem_ld8(t_o + c0, o);
                   ptx::tmem_wait_ld();
@@ -625,15 +577,46 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                   ptx::tmem_st8(t_o + c0, o);
                 }
               }
-              pass = 2;
+              if (q > 0) {    // P chunks 0..q-1 of this tile were formed against the old reference
+                sum[0] = sum[1] = sum[2] = sum[3] = 0.0f;
+                ptx::tmem_wait_st();
+#pragma unroll 1
+                for (int j = 0; j < q; ++j) {
+                  uint32_t w[8];
+                  ptx::tmem_ld8(t_p + 8 * j, w);
+                  ptx::tmem_wait_ld();
+#pragma unroll
+                  for (int x = 0; x < 8; ++x) {
+                    w[x] = Pack2<T>::scale2(w[x], corr);
+                    sum[x & 3] += Pack2<T>::sum2(w[x]);
+                  }
+                  ptx::tmem_st8(t_p + 8 * j, w);
+                }
+              }
             }
+            const float neg_m = -(m_run == -INFINITY ? 0.0f : m_run) * cscale;
+            uint32_t packed[8];
+            // staged by kind of instruction (arguments, exp2, packing, sums): a warp issues in order
+#pragma unroll
+            for (int x = 0; x < 16; ++x) s[x] = fmaf(s[x], cscale, neg_m);
+#pragma unroll
+            for (int x = 0; x < 16; ++x) s[x] = ptx::ex2_approx(s[x]);
+#pragma unroll
+            for (int x = 0; x < 16; x += 2) packed[x / 2] = Pack2<T>::pack(s[x], s[x + 1]);
+            // The row sum is taken over P as rounded for the tensor core, so that the weights P/l the output is
+            // built from sum to one exactly.  (The reference sums the unrounded values, kernel.py:316-333; with the
+            // lazy reference maximum the largest P of a row is not the exactly representable 1.0, and an unrounded
+            // sum would leave the rounding error of the dominant key uncompensated.)
+#pragma unroll
+            for (int x = 0; x < 8; ++x) sum[x & 3] += Pack2<T>::sum2(packed[x]);
+            ptx::tmem_st8(t_p + 8 * q, packed);
           }
+          l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
           TRACE(4);
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
           __syncwarp();
           if (lane == 0) {
-            ptx::mbar_arrive(&bars->s_free[g]);
             if (has_c2p) ptx::mbar_arrive(&bars->ring_release[g]);
             if (has_p2c) ptx::mbar_arrive(&bars->pt_release[g]);
             ptx::mbar_arrive(&bars->p_full[g]);

@@ -48,6 +48,11 @@ struct Pack2<__half> {
     const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
     return f.x + f.y;
   }
+  // both packed values times c, rounded again
+  static __device__ __forceinline__ uint32_t scale2(uint32_t w, float c) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    return pack(f.x * c, f.y * c);
+  }
 };
 template <>
 struct Pack2<__nv_bfloat16> {
@@ -62,6 +67,9 @@ struct Pack2<__nv_bfloat16> {
   }
   static __device__ __forceinline__ float sum2(uint32_t w) {
     return __uint_as_float(w << 16) + __uint_as_float(w & 0xffff0000u);
+  }
+  static __device__ __forceinline__ uint32_t scale2(uint32_t w, float c) {
+    return pack(__uint_as_float(w << 16) * c, __uint_as_float(w & 0xffff0000u) * c);
   }
 };
 
