@@ -282,13 +282,15 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     uint32_t c_t0 = 0, c_t1 = 0;               // tiles seen per stream
     bool ok = true;
 
-    // 64 fp32 columns at t_src -> 64 16-bit values at dst (4-byte aligned), rounded like a GEMM epilogue
-    // (both halves are in flight before the single wait: a TMEM round trip costs several hundred cycles)
-    auto convert_64 = [&](uint32_t t_src, unsigned char* dst, bool mirror) {
-      uint32_t raw0[32], raw1[32];
+    // 64 fp32 columns of this thread's TMEM lane -> registers (both halves in flight before the single wait: a TMEM
+    // round trip costs several hundred cycles), then -> 64 16-bit values at dst (4-byte aligned), rounded like a
+    // GEMM epilogue.  Split in two so that the TMEM buffer can be handed back between the two steps.
+    auto load_64 = [&](uint32_t t_src, uint32_t (&raw0)[32], uint32_t (&raw1)[32]) {
       ptx::tmem_ld32(t_src, raw0);
       ptx::tmem_ld32(t_src + 32, raw1);
       ptx::tmem_wait_ld();
+    };
+    auto store_64 = [&](const uint32_t (&raw0)[32], const uint32_t (&raw1)[32], unsigned char* dst, bool mirror) {
 #pragma unroll
       for (int x = 0; x < 32; x += 2) {
         const uint32_t w = Pack2<T>::pack(__uint_as_float(raw0[x]), __uint_as_float(raw0[x + 1]));
@@ -312,22 +314,27 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const int g = u & 1;
         const uint32_t c_t = g ? c_t1 : c_t0;
         if (has_c2p) {
-          // The ring position a new block overwrites was last read by the stream's previous tile; the first tile of
-          // an item also overwrites positions the other stream's last tile of the previous item read.
-          ok = ptx::mbar_wait_inline(&bars->ring_release[g], (c_t & 1u) ^ 1u, abort_flag, status_word, 17);
-          if (ok && u == 0) ok = ptx::mbar_wait_inline(&bars->ring_release[1], (c_t1 & 1u) ^ 1u, abort_flag, status_word, 17);
-          if (!ok) break;
           const int jobs = u == 0 ? 3 : 1;
           for (int x = 0; x < jobs && ok; ++x, ++c_blk) {
             ok = ptx::mbar_wait_inline(&bars->cnew_full, c_blk & 1u, abort_flag, status_word, 18);
             if (!ok) break;
             TRACE(12);
             ptx::tc_fence_after();
-            const int pos = c_blk & 3;
-            convert_64(tmem_base + lane_base + COL_CNEW, ring_row + pos * 128, pos == 0);
+            uint32_t raw0[32], raw1[32];
+            load_64(tmem_base + lane_base + COL_CNEW, raw0, raw1);
+            // the accumulator is free as soon as it is in registers: the next block's MMA overlaps the stores
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&bars->cnew_free);
+            if (x == 0) {
+              // The ring position a new block overwrites was last read by the stream's previous tile; the first
+              // tile of an item also overwrites positions the other stream's last tile of the previous item read.
+              ok = ptx::mbar_wait_inline(&bars->ring_release[g], (c_t & 1u) ^ 1u, abort_flag, status_word, 17);
+              if (ok && u == 0) ok = ptx::mbar_wait_inline(&bars->ring_release[1], (c_t1 & 1u) ^ 1u, abort_flag, status_word, 17);
+              if (!ok) break;
+            }
+            const int pos = c_blk & 3;
+            store_64(raw0, raw1, ring_row + pos * 128, pos == 0);
             TRACE(13);
           }
           if (!ok) break;
@@ -339,21 +346,32 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           if (!ok) break;
           TRACE(14);
           ptx::tc_fence_after();
-          // the stream's staging tile must have been gathered by the stream's previous tile
-          ok = ptx::mbar_wait_inline(&bars->pt_release[g], (c_t & 1u) ^ 1u, abort_flag, status_word, 20);
-          if (!ok) break;
-          TRACE(15);
           const int pp = c_win & 3;
           unsigned char* stage = smem + LO::offPT + g * LO::kPTStage;
-          convert_64(tmem_base + lane_base + COL_PT, stage + ((pp == 3 ? 64 : 0) + row) * (PT_PITCH_H * 2), false);
-          if (q4 < 2)
-            convert_64(tmem_base + lane_base + COL_PT + BN, stage + ((pp == 3 ? 0 : 128) + row) * (PT_PITCH_H * 2), false);
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) {
-            ptx::mbar_arrive(&bars->pt_free);
-            ptx::mbar_arrive(&bars->pt_ready[g]);
+          {
+            uint32_t raw0[32], raw1[32];
+            load_64(tmem_base + lane_base + COL_PT, raw0, raw1);
+            if (q4 >= 2) {   // these warps are done with the accumulators
+              ptx::tc_fence_before();
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive(&bars->pt_free);
+            }
+            // the stream's staging tile must have been gathered by the stream's previous tile
+            ok = ptx::mbar_wait_inline(&bars->pt_release[g], (c_t & 1u) ^ 1u, abort_flag, status_word, 20);
+            if (!ok) break;
+            TRACE(15);
+            store_64(raw0, raw1, stage + ((pp == 3 ? 64 : 0) + row) * (PT_PITCH_H * 2), false);
           }
+          if (q4 < 2) {
+            uint32_t raw0[32], raw1[32];
+            load_64(tmem_base + lane_base + COL_PT + BN, raw0, raw1);
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&bars->pt_free);
+            store_64(raw0, raw1, stage + ((pp == 3 ? 0 : 128) + row) * (PT_PITCH_H * 2), false);
+          }
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&bars->pt_ready[g]);
           ++c_pt;
           c_win += (u == n - 1) ? 3u : 1u;
           TRACE(16);
