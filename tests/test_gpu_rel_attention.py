@@ -141,3 +141,37 @@ def test_rel_kernel_padded_rows_uniform_deterministic_and_unsupported():
     with pytest.raises(c.DflError, match="not covered"):
         rel = torch.zeros(1, 127, 128, dtype=torch.float16, device=dev)
         c.attention_rel_fwd(big["q"].to(dev), big["k"].to(dev), big["v"].to(dev), rel, rel, big["mask"].to(dev), 0.1)
+
+
+def test_module_plan_carries_rel_tables_where_the_kernel_applies():
+    import disentangled_flash_b200 as df
+
+    def plan_of(dtype, head_dim, length):
+        cfg = df.DebertaAttentionConfig(hidden_size=4 * head_dim, num_attention_heads=4, max_position_embeddings=512,
+                                        position_buckets=256, share_att_key=True, pos_att_type=("p2c", "c2p"),
+                                        norm_rel_ebd="none")
+        module = df.DisentangledFlashAttention(cfg).to(device=dev, dtype=dtype).eval()
+        rel = torch.randn(512, 4 * head_dim, device=dev, dtype=dtype)
+        with torch.inference_mode():
+            module.prepare_for_inference(rel)
+            return module, module.prepare_shape(length, dev)
+
+    module, plan = plan_of(torch.float16, 64, 96)
+    assert plan.rel_key is not None and plan.rel_key.shape == (4, 2 * 96 - 1, 64)
+    assert plan.rel_query is not None and plan.rel_query.dtype == torch.float16
+    lut = plan.delta_to_local.long()
+    assert torch.equal(plan.rel_key, plan.pos_key[:, lut.flip(0), :])
+    # the prepared forward runs through the single-launch kernel and agrees with the two-call path
+    hidden = torch.randn(3, 96, 256, device=dev, dtype=torch.float16)
+    mask = torch.ones(3, 96, dtype=torch.bool, device=dev)
+    mask[1, 70:] = False
+    with torch.inference_mode():
+        got, _ = module.forward_prepared(hidden, mask, plan)
+        bare = plan._replace(rel_key=None, rel_query=None)
+        two, _ = module.forward_prepared(hidden, mask, bare)
+    err = (got.float() - two.float()).abs().cpu().double()
+    assert (err <= 2 * tolerance(torch.float16, two.float().cpu())).all(), err.max().item()
+
+    for dtype, head_dim in ((torch.float32, 64), (torch.float16, 128)):
+        _, other = plan_of(dtype, head_dim, 96)
+        assert other.rel_key is None and other.rel_query is None
