@@ -951,20 +951,24 @@ int launch_rel_typed(const DflAttnRelParams& p, cudaStream_t stream) {
   if (rc != DFL_OK) return rc;
 
   auto kernel = attention_rel_kernel<T, D>;
-  static int sm_count = 0;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LO::total);
+  // one-time configuration per device (the opt-in to large dynamic shared memory is a per-device attribute)
+  constexpr int kMaxDevices = 64;
+  static int sm_counts[kMaxDevices] = {0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) return fail(DFL_ERR_LAUNCH, "current device: %s", cudaGetErrorString(e));
+  if (sm_counts[dev] == 0) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LO::total);
     if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "attention_rel smem opt-in: %s", cudaGetErrorString(e));
-    int dev = 0;
-    e = cudaGetDevice(&dev);
-    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess || sm_count < 1) return fail(DFL_ERR_LAUNCH, "SM count: %s", cudaGetErrorString(e));
-    configured = true;
+    int count = 0;
+    e = cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess || count < 1) return fail(DFL_ERR_LAUNCH, "SM count: %s", cudaGetErrorString(e));
+    sm_counts[dev] = count;
   }
+  const int sm_count = sm_counts[dev];
   int* status_word = p.status;
   if (!status_word) {
-    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status_word), g_attn_rel_status);
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status_word), g_attn_rel_status);
     if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "status word: %s", cudaGetErrorString(e));
   }
   const long long n_items = (long long)BH * ((L + BM - 1) / BM);
