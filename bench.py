@@ -229,7 +229,7 @@ def run_reference_arm(args) -> None:
         "e2e": {"value": value, "unit": "sequences/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    emit(json.dumps(line))
 
 
 def workload_config(args, note: str | None = None):
@@ -437,12 +437,34 @@ def run_gpu_arm(args) -> None:
             "clocks": clocks,
             "rank_checksums": [float(c.item()) for c in checks],
         }
-        print(json.dumps(line))
+        emit(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
 
+_RESULT_FD = None
+
+
+def reserve_stdout() -> None:
+    """Keep stdout for the one JSON line: whatever libraries write to file descriptor 1 meanwhile (NCCL prints its
+    version banner there) goes to stderr instead."""
+
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(text: str) -> None:
+    if _RESULT_FD is None:
+        print(text, flush=True)
+        return
+    sys.stdout.flush()
+    os.write(_RESULT_FD, (text + "\n").encode())
+
+
 def main() -> None:
+    reserve_stdout()
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=20)
