@@ -79,8 +79,12 @@ struct RLayout {
   static constexpr int kPTStage = PT_ROWS * PT_PITCH_H * 2;
   static constexpr int offBar = (offPT + 2 * kPTStage + 15) & ~15;
   static constexpr int kBarBytes = 512;
-  static constexpr int offXchg = offBar + kBarBytes;   // [2 streams][BM] (max, sum); also the mean-of-V scratch
-  static constexpr int kXchgBytes = 2 * BM * 8 + 256;   // + the [D] column mean of the mean-of-V path
+  // two exchange slots (by item parity) of [2 streams][BM] (max, sum); then the mean-of-V scratch: [256] partial
+  // sums and the [D] column mean
+  static constexpr int offXchg = offBar + kBarBytes;
+  static constexpr int kXchgSlot = 2 * BM * 8;
+  static constexpr int offMeanV = offXchg + 2 * kXchgSlot;
+  static constexpr int kXchgBytes = 2 * kXchgSlot + 1024 + 256;
   static constexpr int offItem = offXchg + kXchgBytes; // 2 item slots
   static constexpr int kItemBytes = 160;
   static constexpr int total = offItem + 2 * kItemBytes + 1024;   // + alignment slack
@@ -404,6 +408,9 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       const ItemSlot* sl = &slots[slot];
       if (sl->any_kept != 0) {
         const int n = sl->t_end - sl->t_begin;
+        // O[g] is overwritten by the stream's first PV of an item: the previous item's merge (item k-1 of this CTA,
+        // whatever its kind) must have read both accumulators
+        if (k > 0 && g < n) ok = ptx::mbar_wait_inline(&bars->xbar_b, (uint32_t)(k - 1) & 1u, abort_flag, status_word, 38);
         for (int u = g; u < n && ok; u += 2, ++c_t) {
           const uint32_t tile = c_tiles0 + (uint32_t)u, vb = tile & 1u;
           ok = ptx::mbar_wait_inline(&bars->p_full[g], c_t & 1u, abort_flag, status_word, 7) &&
@@ -440,7 +447,7 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const uint32_t ring_addr = ptx::smem_u32(smem + LO::offRing) + (uint32_t)(r * RING_PITCH_H * 2);
     // PT[m][n] with m = n - r + 128: element n of this row sits at pt_addr + n * (pitch + 1) halfs
     const uint32_t pt_addr = ptx::smem_u32(smem + LO::offPT + g * LO::kPTStage) + (uint32_t)((128 - r) * PT_PITCH_H * 2);
-    float2* xchg = reinterpret_cast<float2*>(smem + LO::offXchg);
+    float2* xchg_base = reinterpret_cast<float2*>(smem + LO::offXchg);
     uint32_t c_t = 0, c_o = 0;      // tiles of this stream / of the other stream so far
     uint32_t c_blk0 = 0;            // C2P blocks produced before this item
     uint32_t c_m = 0;               // items merged
@@ -460,8 +467,8 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       if (!any_kept) {
         // Every query row of this tile is padding: each attends uniformly to all L keys, so every output row is
         // the column mean of V.  No score, no softmax: one pass over V by the 256 softmax threads.
-        float* part = reinterpret_cast<float*>(smem + LO::offXchg);          // [groups][D] partial sums
-        T* mean = reinterpret_cast<T*>(smem + LO::offXchg + 2 * BM * 8);      // [D]
+        float* part = reinterpret_cast<float*>(smem + LO::offMeanV);         // [groups][D] partial sums
+        T* mean = reinterpret_cast<T*>(smem + LO::offMeanV + 1024);          // [D]
         constexpr int kGroups = 256 / D;
         const int tid = threadIdx.x, col = tid % D, grp = tid / D;
         const T* V = reinterpret_cast<const T*>(p.v) + (long long)bh * L * D;
@@ -652,6 +659,7 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         if (ok && other_tiles > 0)
           ok = ptx::mbar_wait_inline(&bars->o_ready[1 - g], (c_o & 1u) ^ 1u, abort_flag, status_word, 24);
         if (!ok) break;
+        float2* xchg = xchg_base + (c_m & 1u) * (2 * BM);   // slots alternate: a stream may be one item ahead
         xchg[g * BM + r] = make_float2(m_run, l_run);
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&bars->xbar_a);
@@ -669,6 +677,11 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         if (my_tiles > 0) attn::tmem_ld_n(t_o + g * HW, o_me);
         if (other_tiles > 0) attn::tmem_ld_n(t_o_other + g * HW, o_ot);
         ptx::tmem_wait_ld();
+        // Both accumulators are in registers: the PV issuer may start the next item's accumulation (it waits for the
+        // eight arrivals); the streams themselves go on without waiting for each other's stores.
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&bars->xbar_b);
         float res[HW];
 #pragma unroll
         for (int x = 0; x < HW; ++x) {
@@ -688,12 +701,6 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             *reinterpret_cast<uint4*>(out + v * 8) = pk;
           }
         }
-        // nobody may start the next item's accumulators or exchange slots before every row has been read
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&bars->xbar_b);
-        ok = ptx::mbar_wait_inline(&bars->xbar_b, c_m & 1u, abort_flag, status_word, 35);
-        if (!ok) break;
         ++c_m;
         TRACE(7);
         if (has_c2p) c_blk0 += (uint32_t)n + 2u;
