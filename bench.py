@@ -373,9 +373,9 @@ def run_gpu_arm(args) -> None:
     peaks, peak_kind = measured_peaks()
     peak = float(peaks.get("bf16_tflops_sustained") or peaks.get("bf16_tflops"))
     # DRAM traffic per launch: dram__bytes_read + dram__bytes_write of one ncu capture of this kernel at B=48, one
-    # layer, same masks (183.39 MB; the summary of that capture is kept under profiles/); traffic is proportional
+    # layer, same masks (182.37 MB; the summary of that capture is kept under profiles/); traffic is proportional
     # to the batch, so it is scaled to this run's batch.  Only valid for the workload geometry it was captured on.
-    traffic = 183.39e6 / 48.0 * B if in_kernel_scores and (H, L, d) == (12, 512, 64) else None
+    traffic = 182.37e6 / 48.0 * B if in_kernel_scores and (H, L, d) == (12, 512, 64) else None
     roofline = {"bound": "tensor", "kernel": observer.kernel_name, "achieved": achieved, "peak": peak,
                 "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
                 "traffic_source": "ncu capture at B=48 scaled by batch" if traffic else None,
