@@ -3,26 +3,33 @@
 // Same result as dfl_pos_scores + dfl_attention_fwd (reference: the two torch.matmul calls at
 // src/disentangled_flash/kernel.py:574-585 followed by the Triton kernel kernel.py:137-345).  The tables
 // rel_key / rel_query [H, 2L-1, d] hold, in row e, the position projection every (query i, key j) pair with
-// x = j - i = e - (L-1) uses, so the two relative terms of a (128 query x 64 key) tile are
+// x = j - i = e - (L-1) uses, so the two relative terms of a (128 query x 128 key) tile are
 //   C2P[i, j] = q_i . rel_key[x]      P2C[i, j] = k_j . rel_query[x]
-// with x running over one contiguous window of 191 table rows.  Both are produced by tcgen05.mma from
-// 64-row table blocks (L2 resident), rounded to the input type exactly like the separate score GEMMs round
-// their output, and parked in shared memory, where the softmax threads pick them up along diagonals.
-//   C2P depends on the query rows only: per query row a ring of four 64-column blocks is kept across key
-//       tiles (a key tile needs one new block; the first tile of an item three).
-//   P2C is new for every key tile: PT[m, n] = rel_query[x_lo + m] . k_n (two 128x64xd MMAs over a ring of four
-//       table blocks, three of them live), so that TMEM lanes are table rows and all lanes convert.
+// with x running over one contiguous window of 255 table rows.  Both are produced by tcgen05.mma from 128-row
+// table blocks (L2 resident), rounded to the input type exactly like the separate score GEMMs round their output,
+// and parked in shared memory, where the softmax threads pick them up along diagonals.
+//   C2P depends on the query rows only: D[r, m] = q_r . rel_key[x_lo + m] with TMEM lanes = query rows.  Per query
+//       row a shared-memory ring of two 128-column blocks is kept (the window of a key tile is two blocks; the next
+//       key tile needs one new block, written in place of the block that left the window).
+//   P2C is new for every key tile: D[n, m] = k_n . rel_query[x_lo + m] with TMEM lanes = keys n, computed in two
+//       halves of 128 table rows through one 128-column accumulator.  Converter warps round each key's row and
+//       store the 136-column span the 128 queries of the tile can reach; a softmax thread then reads, for key n,
+//       element (n & 7) + 128 - r of row n: the 32 lanes of a warp read 32 consecutive elements.
 //
-// Persistent: one CTA per SM walks (batch, head, query tile) items; every role keeps running counters so that
-// the barrier phases carry over from item to item and the loader / MMA issuer run ahead into the next item.
-// Sixteen warps:
-//   warps 0-3   softmax stream 0: one thread per query row, key tiles 0, 2, 4, ... of the item
-//   warps 4-7   softmax stream 1: key tiles 1, 3, 5, ...  Each stream has its own running maximum, row sum and
-//               output accumulator in TMEM (no per-tile exchange); the two are merged once per item.
-//   warps 8-11  converters: TMEM -> 16-bit -> shared memory for the C2P blocks and the PT tiles
-//   warps 12-13 PV issuers, one per stream: O[g] (+)= P[g] V as soon as the stream has stored P
-//   warp 14     per-item mask analysis (kept-key bits, skipped key tiles) and TMA producer
-//   warp 15     issuer of the "front" MMAs of a tile (new C2P block, PT, S) and TMEM owner
+// Persistent: one CTA per SM walks (batch, head, 128-query tile) items in 128-key tiles; every role keeps running
+// counters so that the barrier phases carry over from item to item and the loader / MMA issuer run ahead.
+//   warps 0-7   softmax: two threads per query row (warps w and w+4 own the same TMEM lanes; each takes 64 of the
+//               128 keys of a tile, 32 of the 64 packed P columns and half of the output columns).  Two passes over
+//               the keys in rolled loops of 32: scores + relative terms + mask + maximum, written back to the S
+//               columns; then exp2, rounding, row sum and the P store.
+//   warps 8-11  converters for the C2P block and P2C accumulators (TMEM -> 16-bit -> shared memory)
+//   warp 12     issuer of every MMA (C2P block, S, P2C halves, PV) and TMEM owner
+//   warp 13     per-item mask analysis (kept-key bits, skipped key tiles), one item ahead, and TMA producer
+// The first MMAs of an item (first C2P block, S and P2C of its first key tile) are issued while the softmax threads
+// still work on the last key tile of the previous item; the second C2P block of an item goes through the P and O
+// columns, which are idle between the read-out of one item and the first PV of the next.
+//   warps 14-15 idle (they complete the fourth warpgroup, whose registers go to the softmax warps)
+#include <mutex>
 #include <type_traits>
 
 #include "attention_tc_common.cuh"
@@ -33,61 +40,67 @@ __device__ int g_attn_rel_status = 0;
 
 namespace {
 
-using attn::BM;
-using attn::BN;
 using attn::Pack2;
 
+constexpr int BM = 128;              // query rows per item (= TMEM lanes)
+constexpr int BK = 128;              // keys per tile
 constexpr int kSoftmaxWarps = 8;
-constexpr int kConvHiWarp0 = 12;      // end of the converter warps
-constexpr int kPvWarp0 = 12;
-constexpr int kTmaWarp = 14;
-constexpr int kMmaWarp = 15;
+constexpr int kMmaWarp = 12;
+constexpr int kTmaWarp = 13;
 constexpr int kThreads = 512;
-constexpr int kSoftmaxRegs = 176;   // 256 threads x 176 + 256 threads x 80 = 65536 registers
-constexpr int kOtherRegs = 80;
+constexpr int kSoftmaxRegs = 152;    // 256 x 152 + 128 x 120 + 128 x 88 = 65536 registers
+constexpr int kConvRegs = 120;
+constexpr int kMiscRegs = 88;
+constexpr int kConsumerWarps = 13;   // softmax, converters, MMA issuer: every warp that reads an item slot
 
-constexpr int RING_COLS = 256;                 // four 64-column blocks per query row
-constexpr int RING_MIRROR = 16;                // columns 0..15 repeated at 256..271: a 16-key run never wraps
-constexpr int RING_PITCH_H = 290;              // halfs per ring row (bank spread of the diagonal reads: 1.5 wavefronts)
-constexpr int PT_ROWS = 192;
-constexpr int PT_PITCH_H = BN + 2;             // 33 words: the anti-diagonal reads are conflict free
-constexpr int kMaxSeqLen = 1024;               // 32 words of kept-key bits per item
+constexpr int kItemSlots = 3;        // the loader analyses one item ahead of the one whose tiles it loads
+constexpr int kMaxSeqLen = 2048;
+constexpr int kMaskWords = kMaxSeqLen / 32;   // kept-key bits per item
+
+// C2P ring: per query row two 128-column blocks and the first 16 columns once more (a 16-key run never wraps).
+// 580 bytes = 145 words per row: the diagonal 16-bit reads of a warp and its 32-bit stores are conflict free.
+constexpr int RING_COLS = 256;
+constexpr int RING_MIRROR = 16;
+constexpr int RING_PITCH = 580;
+// P2C staging: per key 17 chunks of 8 columns (the chunk-aligned span of table rows its 128 queries reach).
+// 272 bytes = 68 words per row: eight consecutive rows cover all 32 banks with their 16-byte stores.
+constexpr int STG_CHUNKS = 17;
+constexpr int STG_PITCH = STG_CHUNKS * 16;
 
 // TMEM columns (all 512; one CTA per SM)
-constexpr int COL_S = 0;       // 2 x 64   S of stream 0 / 1
-constexpr int COL_P = 128;     // 2 x 32   P (16-bit pairs) of stream 0 / 1
-constexpr int COL_O = 192;     // 2 x 64   O of stream 0 / 1 (first D columns used)
-constexpr int COL_CNEW = 320;  // 64       one C2P block for 128 query rows
-constexpr int COL_PT = 384;    // 2 x 64   PT accumulators
+constexpr int COL_S = 0;      // 128  S = Q K^T of the current tile (fp32)
+constexpr int COL_P = 128;    // 64   P of the current tile (16-bit pairs), A operand of the PV MMA
+constexpr int COL_O = 192;    // 64   O accumulator (first D columns used)
+constexpr int COL_XC = 256;   // 128  one new C2P block for the 128 query rows
+constexpr int COL_XP = 384;   // 128  one half (128 table rows) of the P2C accumulator of a key tile
 constexpr int kTmemCols = 512;
 
 template <int D>
 struct RLayout {
   static_assert(D == 32 || D == 64, "head dims 32 and 64");
   static constexpr int kRowBytes = D * 2;
-  static constexpr int kQ = BM * kRowBytes;     // Q tile
-  static constexpr int kBlk = BN * kRowBytes;   // K tile, V tile, one 64-row table block
+  static constexpr int kTile = 128 * kRowBytes;        // Q tile, K tile, V tile, one 128-row table block
+  static constexpr int kVStages = D == 64 ? 1 : 2;     // d = 64 fills shared memory: V and rel_key blocks are
+  static constexpr int kRkStages = D == 64 ? 1 : 2;    // reloaded within the tile time after their single use
   static constexpr int offQ = 0;
-  static constexpr int offK = offQ + kQ;              // 2 stages
-  static constexpr int offV = offK + 2 * kBlk;        // 2 stages
-  static constexpr int offPK = offV + 2 * kBlk;       // 2 rel_key blocks
-  static constexpr int offFQ = offPK + 2 * kBlk;      // ring of 4 rel_query blocks
-  // The second PT MMA reads 128 operand rows from a 64-row block; the rows past it (the next block, or the start
-  // of the C2P ring after the last block) only feed TMEM lanes 64..127, which nobody reads.
-  static constexpr int offRing = offFQ + 4 * kBlk;                 // C2P ring [128][RING_PITCH_H]
-  static constexpr int offPT = offRing + BM * RING_PITCH_H * 2;    // PT staging, one per stream
-  static constexpr int kPTStage = PT_ROWS * PT_PITCH_H * 2;
-  static constexpr int offBar = (offPT + 2 * kPTStage + 15) & ~15;
+  static constexpr int offK = offQ + kTile;                 // 2 stages
+  static constexpr int offV = offK + 2 * kTile;
+  static constexpr int offRK = offV + kVStages * kTile;
+  static constexpr int offRQ = offRK + kRkStages * kTile;   // 2 stages
+  static constexpr int offRing = offRQ + 2 * kTile;
+  static constexpr int offStg = offRing + BM * RING_PITCH;
+  static constexpr int offBar = offStg + BK * STG_PITCH;
   static constexpr int kBarBytes = 512;
-  // two exchange slots (by item parity) of [2 streams][BM] (max, sum); then the mean-of-V scratch: [256] partial
-  // sums and the [D] column mean
-  static constexpr int offXchg = offBar + kBarBytes;
-  static constexpr int kXchgSlot = 2 * BM * 8;
-  static constexpr int offMeanV = offXchg + 2 * kXchgSlot;
-  static constexpr int kXchgBytes = 2 * kXchgSlot + 1024 + 256;
-  static constexpr int offItem = offXchg + kXchgBytes; // 2 item slots
-  static constexpr int kItemBytes = 160;
-  static constexpr int total = offItem + 2 * kItemBytes + 1024;   // + alignment slack
+  // exchange area: row maxima [2 parities][2 halves][BM], row sums [2 halves][BM], then the mean-of-V scratch
+  // ([256 / D groups][D] partial sums, [D] column mean)
+  static constexpr int offXmax = offBar + kBarBytes;
+  static constexpr int offXsum = offXmax + 2 * 2 * BM * 4;
+  static constexpr int offMeanV = offXsum + 2 * BM * 4;
+  static constexpr int offItem = offMeanV + 1024 + 256;
+  static constexpr int kItemBytes = 288;
+  static constexpr int total = offItem + kItemSlots * kItemBytes + 1024;   // + alignment slack
+  static_assert(offStg % 16 == 0 && offBar % 16 == 0 && offItem % 16 == 0, "alignment");
+  static_assert(total <= 232448, "shared memory budget");
 };
 
 // What the loader warp publishes per item.
@@ -95,32 +108,36 @@ struct ItemSlot {
   int t_begin, t_end;   // key tiles [t_begin, t_end) are processed
   int any_kept;         // 0: every query row of the tile is padding -> mean-of-V path, no pipeline work
   int bh, i0;           // batch*heads + head, first query row
-  uint32_t kbits[32];   // kept-key bits of the batch row, word w = keys [32w, 32w+32)
+  uint32_t kbits[kMaskWords];   // kept-key bits of the batch row, word w = keys [32w, 32w+32)
 };
-static_assert(sizeof(ItemSlot) <= 160, "item slot too large");
+static_assert(sizeof(ItemSlot) <= 288, "item slot too large");
 
 struct RBarriers {
   uint64_t q_full, q_empty;
   uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
-  uint64_t pk_full[2], pk_empty[2];
-  uint64_t fq_full[4], fq_empty[4];
-  uint64_t s_full[2], s_free[2], p_full[2], o_ready[2];
-  uint64_t cnew_full, cnew_free;
-  uint64_t pt_full, pt_free;
-  uint64_t c2p_ready[2], ring_release[2];
-  uint64_t pt_ready[2], pt_release[2];
-  uint64_t item_full[2], item_empty[2];
-  uint64_t xbar_a, xbar_b;
+  uint64_t rk_full[2], rk_empty[2], rq_full[2], rq_empty[2];
+  uint64_t s_full, s_free;          // S accumulator: MMA -> softmax, softmax (8 warps) -> MMA
+  uint64_t xc_full, xc_free;        // C2P block accumulator: MMA -> converters (4 warps) -> MMA
+  uint64_t b1_full;                 // second C2P block of an item, in the P and O columns
+  uint64_t xp_full, xp_free;        // P2C half accumulator: MMA -> converters (4 warps) -> MMA
+  uint64_t pt_ready, pt_release;    // P2C staging tile: converters -> softmax -> converters
+  uint64_t p_full, o_ready, o_free; // P stored (8 warps); PV complete; output accumulator read out (8 warps)
+  uint64_t c2p_ready, ring_release; // C2P ring blocks of a tile: converters -> softmax -> converters
+  uint64_t pair2[4];                // the two warps of a lane quarter: row maximum (row sum) posted
+  uint64_t item_full[kItemSlots], item_empty[kItemSlots];
+  uint64_t xbar;                    // the eight softmax warps (mean-of-V path)
   uint32_t tmem_base;
   int abort_flag;
 };
 static_assert(sizeof(RBarriers) <= 512, "barrier block too large");
 
+template <int N>
 __device__ __forceinline__ void setmaxnreg_inc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
 }
+template <int N>
 __device__ __forceinline__ void setmaxnreg_dec() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 // tcgen05.mma with shared-memory descriptors passed as 32-bit halves (hi is shared by both operands) and the
@@ -134,13 +151,13 @@ __device__ __forceinline__ void umma_ss_lohi(uint32_t d_tmem, uint32_t a_lo, uin
       ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "n"(ACC)
       : "memory");
 }
-template <int ACC>
-__device__ __forceinline__ void umma_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t hi, uint32_t idesc) {
+__device__ __forceinline__ void umma_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                             uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
       "mov.b64 db, {%2, %3};\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "n"(ACC)
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 
@@ -151,12 +168,81 @@ __device__ __forceinline__ uint32_t lds_u16_r32(uint32_t saddr) {
   asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(saddr) : "memory");
   return v;
 }
+__device__ __forceinline__ uint32_t lds_u32(uint32_t saddr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(saddr) : "memory");
+  return v;
+}
+// low 32 bits of {hi, lo} >> amount (amount 0 or 16: one element of a pair of packed 16-bit values)
+__device__ __forceinline__ uint32_t funnel_r(uint32_t lo, uint32_t hi, uint32_t amount) {
+  uint32_t v;
+  asm("shf.r.wrap.b32 %0, %1, %2, %3;" : "=r"(v) : "r"(lo), "r"(hi), "r"(amount));
+  return v;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float m;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(m) : "f"(a), "f"(b), "f"(c));
+  return m;
+}
+__device__ __forceinline__ void sts_u32(uint32_t saddr, uint32_t v) {
+  asm volatile("st.shared.u32 [%0], %1;" ::"r"(saddr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sts_v4(uint32_t saddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 
-// Kept-key bits of batch row b: lane w returns word w (keys [32w, 32w+32)) built from its own 32 mask elements.
-__device__ __forceinline__ uint32_t kept_bits_word(const DflAttnRelParams& p, int b, int lane) {
+// 32 consecutive fp32 TMEM columns of this thread's lane into arr[off .. off+31] (a register array indexed by
+// compile-time constants; no address of the array is taken, so it stays in registers across loop iterations).
+#define DFL_TMEM_LD32_F(taddr, arr, off)                                                                            \
+  asm volatile(                                                                                                     \
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                                     \
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                                     \
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"                     \
+      : "=f"(arr[off + 0]), "=f"(arr[off + 1]), "=f"(arr[off + 2]), "=f"(arr[off + 3]), "=f"(arr[off + 4]),          \
+        "=f"(arr[off + 5]), "=f"(arr[off + 6]), "=f"(arr[off + 7]), "=f"(arr[off + 8]), "=f"(arr[off + 9]),          \
+        "=f"(arr[off + 10]), "=f"(arr[off + 11]), "=f"(arr[off + 12]), "=f"(arr[off + 13]), "=f"(arr[off + 14]),     \
+        "=f"(arr[off + 15]), "=f"(arr[off + 16]), "=f"(arr[off + 17]), "=f"(arr[off + 18]), "=f"(arr[off + 19]),     \
+        "=f"(arr[off + 20]), "=f"(arr[off + 21]), "=f"(arr[off + 22]), "=f"(arr[off + 23]), "=f"(arr[off + 24]),     \
+        "=f"(arr[off + 25]), "=f"(arr[off + 26]), "=f"(arr[off + 27]), "=f"(arr[off + 28]), "=f"(arr[off + 29]),     \
+        "=f"(arr[off + 30]), "=f"(arr[off + 31])                                                                     \
+      : "r"(taddr)                                                                                                  \
+      : "memory")
+
+#define DFL_TMEM_ST32_F(taddr, arr, off)                                                                            \
+  asm volatile(                                                                                                     \
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "                                                               \
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "                                    \
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"                            \
+      ::"r"(taddr), "f"(arr[off + 0]), "f"(arr[off + 1]), "f"(arr[off + 2]), "f"(arr[off + 3]), "f"(arr[off + 4]),   \
+        "f"(arr[off + 5]), "f"(arr[off + 6]), "f"(arr[off + 7]), "f"(arr[off + 8]), "f"(arr[off + 9]),               \
+        "f"(arr[off + 10]), "f"(arr[off + 11]), "f"(arr[off + 12]), "f"(arr[off + 13]), "f"(arr[off + 14]),          \
+        "f"(arr[off + 15]), "f"(arr[off + 16]), "f"(arr[off + 17]), "f"(arr[off + 18]), "f"(arr[off + 19]),          \
+        "f"(arr[off + 20]), "f"(arr[off + 21]), "f"(arr[off + 22]), "f"(arr[off + 23]), "f"(arr[off + 24]),          \
+        "f"(arr[off + 25]), "f"(arr[off + 26]), "f"(arr[off + 27]), "f"(arr[off + 28]), "f"(arr[off + 29]),          \
+        "f"(arr[off + 30]), "f"(arr[off + 31])                                                                       \
+      : "memory")
+
+// s0 += lo half of w, s1 += hi half of w (w = two packed values of type T), in fp32.
+template <typename T>
+__device__ __forceinline__ void add_pair(float& s0, float& s1, uint32_t w);
+template <>
+__device__ __forceinline__ void add_pair<__half>(float& s0, float& s1, uint32_t w) {
+  asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tadd.rn.f32.f16 %0, lo, %0;\n\tadd.rn.f32.f16 %1, hi, %1;\n\t}"
+      : "+f"(s0), "+f"(s1)
+      : "r"(w));
+}
+template <>
+__device__ __forceinline__ void add_pair<__nv_bfloat16>(float& s0, float& s1, uint32_t w) {
+  asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tadd.rn.f32.bf16 %0, lo, %0;\n\tadd.rn.f32.bf16 %1, hi, %1;\n\t}"
+      : "+f"(s0), "+f"(s1)
+      : "r"(w));
+}
+
+// Kept-key bits of batch row b: word w (keys [32w, 32w+32)) built from its 32 mask elements.
+__device__ __forceinline__ uint32_t kept_bits_word(const DflAttnRelParams& p, int b, int w) {
   const int L = p.seq_len;
   uint32_t kb = 0;
-  const int jw = 32 * lane;
+  const int jw = 32 * w;
   const long long base = (long long)b * L + jw;
   if (jw + 32 <= L && p.mask_elem_size == 1 && ((reinterpret_cast<uintptr_t>(p.mask) + base) & 15) == 0) {
     const uint4* m16 = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(p.mask) + base);
@@ -176,23 +262,30 @@ __device__ __forceinline__ uint32_t kept_bits_word(const DflAttnRelParams& p, in
 // Key tiles before the first and after the last kept key contribute nothing to a kept query row (their
 // probabilities are exactly zero) and are skipped; a padded query row attends uniformly to all L keys, so a query
 // tile that contains one walks every key tile.  A tile of padded rows only is the column mean of V (any_kept false).
-// Warp-collective: kb_mine is the lane's kept-key word of the batch row.
+// Warp-collective: lane l holds the kept-key words l (kb_lo) and l + 32 (kb_hi) of the batch row.
 struct TileRange {
   int t_begin, t_end;
   bool any_kept;
 };
-__device__ __forceinline__ TileRange tile_range(uint32_t kb_mine, int i0, int L, int lane) {
-  const int n_kt = (L + BN - 1) / BN;
-  const uint32_t nz = __ballot_sync(0xffffffffu, kb_mine != 0u);
-  const bool in_q = lane >= (i0 >> 5) && lane < (i0 >> 5) + BM / 32;
-  const int rows_here = L - 32 * lane;   // in-range rows of this lane's word
+__device__ __forceinline__ TileRange tile_range(uint32_t kb_lo, uint32_t kb_hi, int i0, int L, int lane) {
+  const int n_kt = (L + BK - 1) / BK;
+  const uint32_t nz_lo = __ballot_sync(0xffffffffu, kb_lo != 0u);
+  const uint32_t nz_hi = __ballot_sync(0xffffffffu, kb_hi != 0u);
+  const int qw = i0 >> 5;                       // first mask word of the query tile (a multiple of 4)
+  const bool q_hi = qw >= 32;
+  const uint32_t kb = q_hi ? kb_hi : kb_lo;
+  const int wl = qw & 31;
+  const bool in_q = lane >= wl && lane < wl + BM / 32;
+  const int rows_here = L - 32 * (lane + (q_hi ? 32 : 0));   // in-range rows of this lane's word
   const uint32_t full = rows_here >= 32 ? 0xffffffffu : (rows_here <= 0 ? 0u : ((1u << rows_here) - 1u));
-  const bool any_kept = __ballot_sync(0xffffffffu, in_q && kb_mine != 0u) != 0u;
-  const bool any_padded = __ballot_sync(0xffffffffu, in_q && (kb_mine & full) != full) != 0u;
+  const bool any_kept = __ballot_sync(0xffffffffu, in_q && kb != 0u) != 0u;
+  const bool any_padded = __ballot_sync(0xffffffffu, in_q && (kb & full) != full) != 0u;
   TileRange r{0, n_kt, any_kept};
-  if (!any_padded && nz != 0u) {
-    r.t_begin = (__ffs(nz) - 1) >> 1;
-    r.t_end = ((31 - __clz(nz)) >> 1) + 1;
+  if (!any_padded && (nz_lo | nz_hi) != 0u) {
+    const int first = nz_lo ? __ffs(nz_lo) - 1 : 32 + __ffs(nz_hi) - 1;
+    const int last = nz_hi ? 32 + 31 - __clz(nz_hi) : 31 - __clz(nz_lo);
+    r.t_begin = first >> 2;
+    r.t_end = (last >> 2) + 1;
   }
   return r;
 }
@@ -213,7 +306,7 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const int L = p.seq_len, H = p.heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool has_c2p = p.rel_key != nullptr, has_p2c = p.rel_query != nullptr;
-  TRACE_DECL
+  int fail_code = 0;   // code of the bounded wait of this thread that expired first, if any
 
   // ------------------------------------------------------------------ setup (once per CTA)
   if (threadIdx.x == 0) {
@@ -224,29 +317,31 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       ptx::mbar_init(&bars->k_empty[s], 1);
       ptx::mbar_init(&bars->v_full[s], 1);
       ptx::mbar_init(&bars->v_empty[s], 1);
-      ptx::mbar_init(&bars->pk_full[s], 1);
-      ptx::mbar_init(&bars->pk_empty[s], 1);
-      ptx::mbar_init(&bars->s_full[s], 1);
-      ptx::mbar_init(&bars->s_free[s], 4);        // one elected lane per warp of the stream
-      ptx::mbar_init(&bars->p_full[s], 4);
-      ptx::mbar_init(&bars->o_ready[s], 1);
-      ptx::mbar_init(&bars->c2p_ready[s], 4);     // converter warps 8-11
-      ptx::mbar_init(&bars->ring_release[s], 4);
-      ptx::mbar_init(&bars->pt_ready[s], 4);      // converter warps 8-11
-      ptx::mbar_init(&bars->pt_release[s], 4);
+      ptx::mbar_init(&bars->rk_full[s], 1);
+      ptx::mbar_init(&bars->rk_empty[s], 1);
+      ptx::mbar_init(&bars->rq_full[s], 1);
+      ptx::mbar_init(&bars->rq_empty[s], 1);
+    }
+    for (int s = 0; s < kItemSlots; ++s) {
       ptx::mbar_init(&bars->item_full[s], 1);
-      ptx::mbar_init(&bars->item_empty[s], 15);   // every warp but the loader
+      ptx::mbar_init(&bars->item_empty[s], kConsumerWarps);
     }
-    for (int s = 0; s < 4; ++s) {
-      ptx::mbar_init(&bars->fq_full[s], 1);
-      ptx::mbar_init(&bars->fq_empty[s], 1);
-    }
-    ptx::mbar_init(&bars->cnew_full, 1);
-    ptx::mbar_init(&bars->cnew_free, 4);
-    ptx::mbar_init(&bars->pt_full, 1);
-    ptx::mbar_init(&bars->pt_free, 4);
-    ptx::mbar_init(&bars->xbar_a, kSoftmaxWarps);
-    ptx::mbar_init(&bars->xbar_b, kSoftmaxWarps);
+    ptx::mbar_init(&bars->b1_full, 1);
+    ptx::mbar_init(&bars->s_full, 1);
+    ptx::mbar_init(&bars->s_free, kSoftmaxWarps);   // one elected lane per softmax warp
+    ptx::mbar_init(&bars->xc_full, 1);
+    ptx::mbar_init(&bars->xc_free, 4);              // converter warps
+    ptx::mbar_init(&bars->xp_full, 1);
+    ptx::mbar_init(&bars->xp_free, 4);              // converter warps
+    ptx::mbar_init(&bars->pt_ready, 4);
+    ptx::mbar_init(&bars->pt_release, kSoftmaxWarps);
+    ptx::mbar_init(&bars->p_full, kSoftmaxWarps);
+    ptx::mbar_init(&bars->o_ready, 1);
+    ptx::mbar_init(&bars->o_free, kSoftmaxWarps);
+    ptx::mbar_init(&bars->c2p_ready, 4);
+    ptx::mbar_init(&bars->ring_release, kSoftmaxWarps);
+    for (int s = 0; s < 4; ++s) ptx::mbar_init(&bars->pair2[s], 2);
+    ptx::mbar_init(&bars->xbar, kSoftmaxWarps);
     bars->abort_flag = 0;
     ptx::fence_mbar_init();
   }
@@ -269,194 +364,43 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   ptx::tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
-  // Items of this CTA: it = blockIdx.x, blockIdx.x + gridDim.x, ...  item -> (query tile, batch*head)
-  // Every role walks the same item sequence and keeps its own running counters.
-
-  // Register budgets are set per warpgroup (warps 0-3, 4-7: softmax; 8-11: converters; 12-15: the rest), at the
-  // head of the branch the whole warpgroup takes.
-  auto converter_role = [&]() {
-    // -------------------------------------------------------------- converters
-    // Thread (quarter q4, lane) owns TMEM lane 32*q4 + lane: a query row of a C2P block, a table row of the first
-    // PT accumulator and, for lanes 0..63 (warps 8 and 9), a table row of the second PT accumulator.
-    const int q4 = warp & 3;
-    const int row = q4 * 32 + lane;
-    const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
-    unsigned char* ring_row = smem + LO::offRing + row * (RING_PITCH_H * 2);
-    uint32_t c_blk = 0, c_pt = 0, c_win = 0;   // C2P blocks converted, PT tiles converted, table-window position
-    uint32_t c_t0 = 0, c_t1 = 0;               // tiles seen per stream
-    bool ok = true;
-
-    // 64 fp32 columns of this thread's TMEM lane -> registers (both halves in flight before the single wait: a TMEM
-    // round trip costs several hundred cycles), then -> 64 16-bit values at dst (4-byte aligned), rounded like a
-    // GEMM epilogue.  Split in two so that the TMEM buffer can be handed back between the two steps.
-    auto load_64 = [&](uint32_t t_src, uint32_t (&raw0)[32], uint32_t (&raw1)[32]) {
-      ptx::tmem_ld32(t_src, raw0);
-      ptx::tmem_ld32(t_src + 32, raw1);
-      ptx::tmem_wait_ld();
-    };
-    auto store_64 = [&](const uint32_t (&raw0)[32], const uint32_t (&raw1)[32], unsigned char* dst, bool mirror) {
-#pragma unroll
-      for (int x = 0; x < 32; x += 2) {
-        const uint32_t w = Pack2<T>::pack(__uint_as_float(raw0[x]), __uint_as_float(raw0[x + 1]));
-        *reinterpret_cast<uint32_t*>(dst + x * 2) = w;
-        if (x < RING_MIRROR && mirror) *reinterpret_cast<uint32_t*>(dst + RING_COLS * 2 + x * 2) = w;
-      }
-#pragma unroll
-      for (int x = 0; x < 32; x += 2)
-        *reinterpret_cast<uint32_t*>(dst + 64 + x * 2) = Pack2<T>::pack(__uint_as_float(raw1[x]), __uint_as_float(raw1[x + 1]));
-    };
-
-    int k = 0;
-    for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++k) {
-      const int slot = k & 1;
-      ok = ptx::mbar_wait_inline(&bars->item_full[slot], (uint32_t)(k >> 1) & 1u, abort_flag, status_word, 32);
-      if (!ok) break;
-      const ItemSlot* sl = &slots[slot];
-      const int n = sl->t_end - sl->t_begin;
-      const bool any_kept = sl->any_kept != 0;
-      for (int u = 0; u < n && ok && any_kept; ++u) {
-        const int g = u & 1;
-        const uint32_t c_t = g ? c_t1 : c_t0;
-        if (has_c2p) {
-          const int jobs = u == 0 ? 3 : 1;
-          for (int x = 0; x < jobs && ok; ++x, ++c_blk) {
-            ok = ptx::mbar_wait_inline(&bars->cnew_full, c_blk & 1u, abort_flag, status_word, 18);
-            if (!ok) break;
-            TRACE(12);
-            ptx::tc_fence_after();
-            uint32_t raw0[32], raw1[32];
-            load_64(tmem_base + lane_base + COL_CNEW, raw0, raw1);
-            // the accumulator is free as soon as it is in registers: the next block's MMA overlaps the stores
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&bars->cnew_free);
-            if (x == 0) {
-              // The ring position a new block overwrites was last read by the stream's previous tile; the first
-              // tile of an item also overwrites positions the other stream's last tile of the previous item read.
-              ok = ptx::mbar_wait_inline(&bars->ring_release[g], (c_t & 1u) ^ 1u, abort_flag, status_word, 17);
-              if (ok && u == 0) ok = ptx::mbar_wait_inline(&bars->ring_release[1], (c_t1 & 1u) ^ 1u, abort_flag, status_word, 17);
-              if (!ok) break;
-            }
-            const int pos = c_blk & 3;
-            store_64(raw0, raw1, ring_row + pos * 128, pos == 0);
-            TRACE(13);
-          }
-          if (!ok) break;
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(&bars->c2p_ready[g]);
-        }
-        if (has_p2c) {
-          ok = ptx::mbar_wait_inline(&bars->pt_full, c_pt & 1u, abort_flag, status_word, 19);
-          if (!ok) break;
-          TRACE(14);
-          ptx::tc_fence_after();
-          const int pp = c_win & 3;
-          unsigned char* stage = smem + LO::offPT + g * LO::kPTStage;
-          {
-            uint32_t raw0[32], raw1[32];
-            load_64(tmem_base + lane_base + COL_PT, raw0, raw1);
-            if (q4 >= 2) {   // these warps are done with the accumulators
-              ptx::tc_fence_before();
-              __syncwarp();
-              if (lane == 0) ptx::mbar_arrive(&bars->pt_free);
-            }
-            // the stream's staging tile must have been gathered by the stream's previous tile
-            ok = ptx::mbar_wait_inline(&bars->pt_release[g], (c_t & 1u) ^ 1u, abort_flag, status_word, 20);
-            if (!ok) break;
-            TRACE(15);
-            store_64(raw0, raw1, stage + ((pp == 3 ? 64 : 0) + row) * (PT_PITCH_H * 2), false);
-          }
-          if (q4 < 2) {
-            uint32_t raw0[32], raw1[32];
-            load_64(tmem_base + lane_base + COL_PT + BN, raw0, raw1);
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&bars->pt_free);
-            store_64(raw0, raw1, stage + ((pp == 3 ? 0 : 128) + row) * (PT_PITCH_H * 2), false);
-          }
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(&bars->pt_ready[g]);
-          ++c_pt;
-          c_win += (u == n - 1) ? 3u : 1u;
-          TRACE(16);
-        }
-        if (g) ++c_t1; else ++c_t0;
-      }
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&bars->item_empty[slot]);
-    }
+  // A bounded wait whose verdict is the same in every lane of the warp (the tcgen05.ld/st/wait instructions that
+  // follow are warp-collective and must not be reached by part of a warp).
+  auto wwait = [&](uint64_t* bar, uint32_t parity, int code) -> bool {
+    return __all_sync(0xffffffffu, ptx::mbar_wait_inline(bar, parity, abort_flag, fail_code, code));
   };
 
-  // Warps 12, 13 (lane 0): PV issuer of stream 0 / 1: O[g] (+)= P[g] . V(tile) once the stream's four warps have stored P.
-  auto pv_role = [&]() {
-    if (lane != 0) return;
-    const int g = warp - kPvWarp0;
-    constexpr int is_bf16 = __is_same(T, __nv_bfloat16) ? 1 : 0;
-    constexpr uint32_t idesc_pv = ptx::make_idesc_f16(is_bf16, BM, D, 0, 1);   // V is MN-major
-    constexpr uint32_t desc_hi = (((8u * LO::kRowBytes) >> 4) & 0x3FFFu) | (1u << 14) |
-                                 (ptx::swizzle_mode_for_row_bytes(LO::kRowBytes) << 29);
-    constexpr uint32_t kStepUnits = (16u * LO::kRowBytes) >> 4;   // 16 keys further down the V tile
-    const uint32_t v_lo = ((ptx::smem_u32(smem + LO::offV) >> 4) & 0x3FFFu) | (((uint32_t)LO::kBlk >> 4) << 16);
-    const uint32_t t_o = tmem_base + COL_O + g * 64, t_p = tmem_base + COL_P + g * (BN / 2);
-    uint32_t c_t = 0, c_tiles0 = 0;   // tiles of this stream so far; tiles of all earlier items
-    bool ok = true;
-    int k = 0;
-    for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++k) {
-      const int slot = k & 1;
-      ok = ptx::mbar_wait_inline(&bars->item_full[slot], (uint32_t)(k >> 1) & 1u, abort_flag, status_word, 36);
-      if (!ok) break;
-      const ItemSlot* sl = &slots[slot];
-      if (sl->any_kept != 0) {
-        const int n = sl->t_end - sl->t_begin;
-        // O[g] is overwritten by the stream's first PV of an item: the previous item's merge (item k-1 of this CTA,
-        // whatever its kind) must have read both accumulators
-        if (k > 0 && g < n) ok = ptx::mbar_wait_inline(&bars->xbar_b, (uint32_t)(k - 1) & 1u, abort_flag, status_word, 38);
-        for (int u = g; u < n && ok; u += 2, ++c_t) {
-          const uint32_t tile = c_tiles0 + (uint32_t)u, vb = tile & 1u;
-          ok = ptx::mbar_wait_inline(&bars->p_full[g], c_t & 1u, abort_flag, status_word, 7) &&
-               ptx::mbar_wait_inline(&bars->v_full[vb], (tile >> 1) & 1u, abort_flag, status_word, 8);
-          if (!ok) break;
-          TRACE(27);
-          ptx::tc_fence_after();
-          const uint32_t vt_lo = v_lo + vb * ((uint32_t)LO::kBlk >> 4);
-          if (u < 2) umma_ts_lohi<0>(t_o, t_p, vt_lo, desc_hi, idesc_pv);
-          else umma_ts_lohi<1>(t_o, t_p, vt_lo, desc_hi, idesc_pv);
-#pragma unroll
-          for (int kk = 1; kk < BN / 16; ++kk)
-            umma_ts_lohi<1>(t_o, t_p + kk * 8, vt_lo + kk * kStepUnits, desc_hi, idesc_pv);
-          ptx::umma_commit(&bars->v_empty[vb]);
-          ptx::umma_commit(&bars->o_ready[g]);
-        }
-        c_tiles0 += (uint32_t)n;
-      }
-      ptx::mbar_arrive(&bars->item_empty[slot]);
-    }
-  };
-
+  // Every role walks the same item sequence (item number k of this CTA is item blockIdx.x + k * gridDim.x; it uses
+  // item slot k % 3 in phase (k / 3) & 1) and keeps its own running counters.  Register budgets are set per
+  // warpgroup (warps 0-3, 4-7: softmax; 8-11: converters; 12-15: the rest), at the head of the branch the whole
+  // warpgroup takes.  The loops over a tile's keys are rolled on purpose: the kernel is bound by instruction fetch
+  // as soon as the code of a tile no longer fits the instruction caches.
   if (warp < kSoftmaxWarps) {
-    setmaxnreg_inc();
+    setmaxnreg_inc<kSoftmaxRegs>();
     // ----------------------------------------------------------------- softmax
-    const int g = warp >> 2, q4 = warp & 3;     // stream, lane quarter
+    const int hf = warp >> 2, q4 = warp & 3;    // key half of the tile, lane quarter
     const int r = q4 * 32 + lane;               // query row of the tile = TMEM lane
     const float cscale = p.scale * 1.4426950408889634f;
+    const float slack = attn::kLazyMaxSlack / cscale;
+    constexpr int OW = D / 2;                   // output columns per thread
     const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
-    const uint32_t t_s = tmem_base + lane_base + COL_S + g * BN;
-    const uint32_t t_p = tmem_base + lane_base + COL_P + g * (BN / 2);
-    const uint32_t t_o = tmem_base + lane_base + COL_O + g * 64;
-    const uint32_t t_o_other = tmem_base + lane_base + COL_O + (1 - g) * 64;
-    const uint32_t ring_addr = ptx::smem_u32(smem + LO::offRing) + (uint32_t)(r * RING_PITCH_H * 2);
-    // PT[m][n] with m = n - r + 128: element n of this row sits at pt_addr + n * (pitch + 1) halfs
-    const uint32_t pt_addr = ptx::smem_u32(smem + LO::offPT + g * LO::kPTStage) + (uint32_t)((128 - r) * PT_PITCH_H * 2);
-    float2* xchg_base = reinterpret_cast<float2*>(smem + LO::offXchg);
-    uint32_t c_t = 0, c_o = 0;      // tiles of this stream / of the other stream so far
-    uint32_t c_blk0 = 0;            // C2P blocks produced before this item
-    uint32_t c_m = 0;               // items merged
+    const uint32_t t_s = tmem_base + lane_base + COL_S + hf * 64;
+    const uint32_t t_p = tmem_base + lane_base + COL_P + hf * 32;
+    const uint32_t t_o = tmem_base + lane_base + COL_O + hf * OW;
+    const uint32_t ring_row = ptx::smem_u32(smem + LO::offRing) + (uint32_t)(r * RING_PITCH);
+    const uint32_t odd16 = (uint32_t)(r & 1) * 16u;   // a row's window starts on an odd column iff r is odd
+    // P2C of (row r, key n) is element (n & 7) + 128 - r of staging row n
+    const uint32_t stg_base = ptx::smem_u32(smem + LO::offStg) + (uint32_t)(hf * 64 * STG_PITCH + 2 * (128 - r));
+    float* xmax = reinterpret_cast<float*>(smem + LO::offXmax);
+    float* xsum = reinterpret_cast<float*>(smem + LO::offXsum);
+    uint64_t* pair2 = &bars->pair2[q4];
+    uint32_t c_s = 0, c_cr = 0, c_pt = 0, c_pv = 0, c_p2 = 0, c_xb = 0;
     bool ok = true;
 
     int k = 0;
     for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++k) {
-      const int slot = k & 1;
-      ok = ptx::mbar_wait_inline(&bars->item_full[slot], (uint32_t)(k >> 1) & 1u, abort_flag, status_word, 33);
+      const int slot = k % kItemSlots;
+      ok = wwait(&bars->item_full[slot], (uint32_t)(k / kItemSlots) & 1u, 33);
       if (!ok) break;
       const ItemSlot* sl = &slots[slot];
       const int t_begin = sl->t_begin, n = sl->t_end - sl->t_begin;
@@ -476,8 +420,9 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         for (int row = grp; row < L; row += kGroups) sum += Elem<T>::to_f(V[(long long)row * D + col]);
         part[grp * D + col] = sum;
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&bars->xbar_a);
-        ok = ptx::mbar_wait_inline(&bars->xbar_a, c_m & 1u, abort_flag, status_word, 34);
+        if (lane == 0) ptx::mbar_arrive(&bars->xbar);
+        ok = wwait(&bars->xbar, c_xb & 1u, 34);
+        ++c_xb;
         if (!ok) break;
         if (tid < D) {
           float total = 0.0f;
@@ -485,10 +430,10 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           mean[tid] = Elem<T>::from_f(total / (float)L);
         }
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&bars->xbar_b);
-        ok = ptx::mbar_wait_inline(&bars->xbar_b, c_m & 1u, abort_flag, status_word, 35);
+        if (lane == 0) ptx::mbar_arrive(&bars->xbar);
+        ok = wwait(&bars->xbar, c_xb & 1u, 35);
+        ++c_xb;
         if (!ok) break;
-        ++c_m;
         const int rows = L - i0 < BM ? L - i0 : BM;
         constexpr int kVec = D / 8;  // 16-byte chunks per output row
         const uint4 mine = *reinterpret_cast<const uint4*>(mean + (tid % kVec) * 8);
@@ -497,430 +442,658 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           const int rr = e / kVec, v = e - rr * kVec;
           *reinterpret_cast<uint4*>(out + (long long)rr * H * D + v * 8) = mine;
         }
+        // keeps the phase of o_free equal to the item count; also orders the next use of the scratch
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&bars->o_free);
       } else {
         const int i = i0 + r;
         const bool row_ok = i < L;
         const bool q_keep = row_ok && ((sl->kbits[i >> 5] >> (i & 31)) & 1u) != 0u;
         float m_run = -INFINITY, l_run = 0.0f;
 
-        for (int u = g; u < n && ok; u += 2) {
-          const int t = t_begin + u, j0 = t * BN;
-          // The stream's previous PV must be complete before its P operand is overwritten or O is rescaled.
-          ok = ptx::mbar_wait_inline(&bars->o_ready[g], (c_t & 1u) ^ 1u, abort_flag, status_word, 22) &&
-               ptx::mbar_wait_inline(&bars->s_full[g], c_t & 1u, abort_flag, status_word, 9);
-          if (ok && has_c2p) ok = ptx::mbar_wait_inline(&bars->c2p_ready[g], c_t & 1u, abort_flag, status_word, 10);
-          if (ok && has_p2c) ok = ptx::mbar_wait_inline(&bars->pt_ready[g], c_t & 1u, abort_flag, status_word, 21);
-          if (!ok) break;
-          TRACE(1);
-          ptx::tc_fence_after();
-          // ring column of (row r, key x of the tile): (64 * block index of the tile + 128 - r + x) mod 256
-          const uint32_t cb = (64u * (c_blk0 + (uint32_t)u) + 128u - (uint32_t)r) & 255u;
-          const uint32_t kb0 = sl->kbits[2 * t], kb1 = sl->kbits[2 * t + 1];
-          const bool keys_all_kept = (kb0 & kb1) == 0xffffffffu;
-          const int n_in = L - j0;
+        for (int u = 0; u < n && ok; ++u) {
+          const int t = t_begin + u;
+          const uint32_t kb0 = sl->kbits[4 * t + 2 * hf], kb1 = sl->kbits[4 * t + 2 * hf + 1];
+          const int n_in = L - t * BK - hf * 64;   // in-range keys among this thread's 64 (may be <= 0 or >= 64)
+          // ring column of (row r, key x of the tile): (128 * (u & 1) + 128 - r + x) mod 256
+          const uint32_t cb = (128u * (uint32_t)(u & 1) + 128u - (uint32_t)r + 64u * (uint32_t)hf) & 255u;
 
-          // The tile is walked in four chunks of 16 keys by one rolled loop (a small loop body stays in the
-          // instruction cache; a fully unrolled 64-key body does not): the two relative terms from shared memory,
-          // mask, exp2 against the running reference maximum, P chunk to TMEM.
-          // One TMEM round trip per tile (a tcgen05.ld -> wait::ld pair costs several hundred cycles, and wait::ld
-          // drains every outstanding load, so per-chunk loads cannot be pipelined): the whole S row is fetched at
-          // once - which also frees the S buffer for the MMA of the stream's next tile right away - and the loop
-          // consumes the first 16 registers, then rotates the rest down.
-          uint32_t raw[BN];
-          {
-            uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[0]);
-            uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[32]);
-            ptx::tmem_ld32(t_s, lo);
-            ptx::tmem_ld32(t_s + 32, hi);
-            ptx::tmem_wait_ld();
+          ok = wwait(&bars->s_full, c_s & 1u, 41);
+          ++c_s;
+          if (ok && has_c2p) {
+            ok = wwait(&bars->c2p_ready, c_cr & 1u, 42);
+            ++c_cr;
           }
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(&bars->s_free[g]);
-          TRACE(2);
+          if (ok && has_p2c) {
+            ok = wwait(&bars->pt_ready, c_pt & 1u, 44);
+            ++c_pt;
+          }
+          if (!ok) break;
+          ptx::tc_fence_after();
 
-          // Lazy reference maximum: m_run moves only when a chunk maximum exceeds it by more than 2^8 after scaling,
-          // so exp2 arguments stay <= 8 (P <= 256, exact range of both 16-bit types) and O needs rescaling rarely.
-          // On a move, everything accumulated against the old reference is rescaled: the row sum, O in TMEM (if the
-          // stream already accumulated in this item) and the P chunks of this tile that are already written.
-          float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+          // ---- pass 1 over the thread's 64 keys in two chunks of 32: S from TMEM (the next chunk in flight), the two
+          // relative terms from shared memory, mask, running maximum; the biased scores go back to the S columns.
+          float cur[32], nxt[32];
+          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          DFL_TMEM_LD32_F(t_s, nxt, 0);
 #pragma unroll 1
-          for (int q = 0; q < 4; ++q) {
-            float s[16];
+          for (int q = 0; q < 2; ++q) {
+            ptx::tmem_wait_ld();
 #pragma unroll
-            for (int x = 0; x < 16; ++x) s[x] = __uint_as_float(raw[x]);
-#pragma unroll
-            for (int x = 0; x < BN - 16; ++x) raw[x] = raw[x + 16];
-            // per term: 16 loads issued before the 16 adds that use them (a warp issues in order; a load followed
-            // at once by its consumer would expose the shared-memory latency once per element)
-            if (has_c2p) {
-              const uint32_t base = (cb + 16u * q) & 255u;   // a 16-key run stays inside columns [base, base+16) <= 271
-              const uint32_t caddr = ring_addr + 2u * base;
-              uint32_t cv[16];
-#pragma unroll
-              for (int x = 0; x < 16; ++x) cv[x] = lds_u16_r32(caddr + 2u * x);
-#pragma unroll
-              for (int x = 0; x < 16; ++x) s[x] = Pack2<T>::add(s[x], (uint16_t)cv[x]);
-            }
+            for (int x = 0; x < 32; ++x) cur[x] = nxt[x];
+            if (q == 0) DFL_TMEM_LD32_F(t_s + 32, nxt, 0);
             if (has_p2c) {
-              const uint32_t paddr = pt_addr + (uint32_t)(q * 16 * (PT_PITCH_H + 1) * 2);
-              uint32_t pv[16];
+              const uint32_t paddr = stg_base + (uint32_t)(q * 32 * STG_PITCH);
 #pragma unroll
-              for (int x = 0; x < 16; ++x) pv[x] = lds_u16_r32(paddr + (uint32_t)(x * (PT_PITCH_H + 1) * 2));
+              for (int j = 0; j < 2; ++j) {
+                // per 16 keys: 16 loads issued before the 16 adds that use them (a warp issues in order)
+                uint32_t pv[16];
 #pragma unroll
-              for (int x = 0; x < 16; ++x) s[x] = Pack2<T>::add(s[x], (uint16_t)pv[x]);
+                for (int x = 0; x < 16; ++x)
+                  pv[x] = lds_u16_r32(paddr + (uint32_t)((16 * j + x) * STG_PITCH + 2 * (x & 7)));
+#pragma unroll
+                for (int x = 0; x < 16; ++x) cur[16 * j + x] = Pack2<T>::add(cur[16 * j + x], (uint16_t)pv[x]);
+              }
+            }
+            if (has_c2p) {
+#pragma unroll
+              for (int j = 0; j < 2; ++j) {
+                // 16 keys are read as nine aligned 32-bit words and shifted by one element where the run starts on
+                // an odd column; the run stays below column 272 (the first 16 columns are mirrored behind the ring)
+                const uint32_t w0 = (cb + 32u * (uint32_t)q + 16u * j) & 255u;
+                const uint32_t caddr = ring_row + 2u * (w0 & ~1u);
+                uint32_t cw[9];
+#pragma unroll
+                for (int x = 0; x < 9; ++x) cw[x] = lds_u32(caddr + 4u * x);
+#pragma unroll
+                for (int x = 0; x < 8; ++x)
+                  add_pair<T>(cur[16 * j + 2 * x], cur[16 * j + 2 * x + 1], funnel_r(cw[x], cw[x + 1], odd16));
+              }
             }
             // mask: keys >= L and padded keys -> -inf; a padded query row -> 0 on every in-range key
+            const uint32_t kbq = q ? kb1 : kb0;
             if (!q_keep) {
+              const int n_q = n_in - 32 * q;
 #pragma unroll
-              for (int x = 0; x < 16; ++x) s[x] = 16 * q + x < n_in ? 0.0f : -INFINITY;
-            } else if (!keys_all_kept) {
-              const uint32_t kbq = ((q < 2 ? kb0 : kb1) >> ((q & 1) * 16)) & 0xffffu;
+              for (int x = 0; x < 32; ++x) cur[x] = x < n_q ? 0.0f : -INFINITY;
+            } else if (kbq != 0xffffffffu) {
 #pragma unroll
-              for (int x = 0; x < 16; ++x)
-                if (!((kbq >> x) & 1u)) s[x] = -INFINITY;
+              for (int x = 0; x < 32; ++x)
+                if (!((kbq >> x) & 1u)) cur[x] = -INFINITY;
             }
-            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int x = 0; x < 16; ++x) mx[x & 3] = fmaxf(mx[x & 3], s[x]);
-            const float cmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-            const bool move = cmax > m_run + attn::kLazyMaxSlack / cscale;  // also true for the first finite maximum
-            if (__any_sync(0xffffffffu, move)) {
-              const float m_new = move ? cmax : m_run;
-              const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-              const float corr = move ? ptx::ex2_approx((m_run - m_use) * cscale) : 1.0f;   // 0 when m_run = -inf
-              m_run = m_new;
-              l_run *= corr;
-              if (u >= 2) {   // the stream already accumulated into O in this item
-#pragma unroll 1
-                for (int c0 = 0; c0 < D; c0 += 8) {   // rare: small rolled steps keep the register footprint low
-                  uint32_t o[8];
-                  ptx::tmem_ld8(t_o + c0, o);
-                  ptx::tmem_wait_ld();
-#pragma unroll
-                  for (int x = 0; x < 8; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * corr);
-                  ptx::tmem_st8(t_o + c0, o);
-                }
-              }
-              if (q > 0) {    // P chunks 0..q-1 of this tile were formed against the old reference
-                sum[0] = sum[1] = sum[2] = sum[3] = 0.0f;
-                ptx::tmem_wait_st();
-#pragma unroll 1
-                for (int j = 0; j < q; ++j) {
-                  uint32_t w[8];
-                  ptx::tmem_ld8(t_p + 8 * j, w);
-                  ptx::tmem_wait_ld();
-#pragma unroll
-                  for (int x = 0; x < 8; ++x) {
-                    w[x] = Pack2<T>::scale2(w[x], corr);
-                    sum[x & 3] += Pack2<T>::sum2(w[x]);
-                  }
-                  ptx::tmem_st8(t_p + 8 * j, w);
-                }
-              }
-            }
-            const float neg_m = -(m_run == -INFINITY ? 0.0f : m_run) * cscale;
-            uint32_t packed[8];
-            // staged by kind of instruction (arguments, exp2, packing, sums): a warp issues in order
-#pragma unroll
-            for (int x = 0; x < 16; ++x) s[x] = fmaf(s[x], cscale, neg_m);
-#pragma unroll
-            for (int x = 0; x < 16; ++x) s[x] = ptx::ex2_approx(s[x]);
-#pragma unroll
-            for (int x = 0; x < 16; x += 2) packed[x / 2] = Pack2<T>::pack(s[x], s[x + 1]);
-            // The row sum is taken over P as rounded for the tensor core, so that the weights P/l the output is
-            // built from sum to one exactly.  (The reference sums the unrounded values, kernel.py:316-333; with the
-            // lazy reference maximum the largest P of a row is not the exactly representable 1.0, and an unrounded
-            // sum would leave the rounding error of the dominant key uncompensated.)
-#pragma unroll
-            for (int x = 0; x < 8; ++x) sum[x & 3] += Pack2<T>::sum2(packed[x]);
-            ptx::tmem_st8(t_p + 8 * q, packed);
+            for (int x = 0; x < 32; x += 2) mx[(x >> 1) & 3] = max3(mx[(x >> 1) & 3], cur[x], cur[x + 1]);
+            DFL_TMEM_ST32_F(t_s + 32 * q, cur, 0);
           }
+          // the ring blocks and the staging tile of this tile are read
+          __syncwarp();
+          if (lane == 0) {
+            if (has_c2p) ptx::mbar_arrive(&bars->ring_release);
+            if (has_p2c) ptx::mbar_arrive(&bars->pt_release);
+          }
+          const float my_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+          // the row maximum of the tile needs the other half of the keys: exchange through shared memory
+          float* xm = xmax + (c_p2 & 1u) * (2 * BM);
+          xm[hf * BM + r] = my_max;
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(pair2);
+          ptx::tmem_wait_st();
+          DFL_TMEM_LD32_F(t_s, nxt, 0);   // first chunk of pass 2, in flight during the exchange
+          ok = wwait(pair2, c_p2 & 1u, 45);
+          ++c_p2;
+          if (!ok) break;
+          const float tile_max = fmaxf(my_max, xm[(1 - hf) * BM + r]);
+
+          // Lazy reference maximum: m_run moves only when the tile maximum exceeds it by more than 2^8 after scaling,
+          // so exp2 arguments stay <= 8 (P <= 256, exact range of both 16-bit types) and O needs rescaling rarely.
+          // Both threads of a row see the same m_run and tile_max and take the same decision.
+          bool pv_seen = false;   // PV(u-1) known complete
+          const bool move = tile_max > m_run + slack;   // also true for the first finite maximum
+          if (__any_sync(0xffffffffu, move)) {
+            const float m_new = move ? tile_max : m_run;
+            const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+            const float corr = move ? ptx::ex2_approx((m_run - m_use) * cscale) : 1.0f;   // 0 when m_run = -inf
+            m_run = m_new;
+            l_run *= corr;
+            if (u >= 1) {   // O holds the item's earlier tiles: rescale this thread's half of the columns
+              ok = wwait(&bars->o_ready, c_pv & 1u, 46);
+              ++c_pv;
+              pv_seen = true;
+              if (!ok) break;
+              ptx::tc_fence_after();
+#pragma unroll
+              for (int c0 = 0; c0 < OW; c0 += 16) {
+                uint32_t o[16];
+                ptx::tmem_ld16(t_o + c0, o);
+                ptx::tmem_wait_ld();
+#pragma unroll
+                for (int x = 0; x < 16; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * corr);
+                ptx::tmem_st16(t_o + c0, o);
+              }
+            }
+          }
+          const float neg_m = -(m_run == -INFINITY ? 0.0f : m_run) * cscale;
+
+          // ---- pass 2: P = exp2(biased score * scale - reference), rounded, to the P columns; row sum.
+          // The row sum is taken over P as rounded for the tensor core, so that the weights P/l the output is
+          // built from sum to one exactly.  (The reference sums the unrounded values, kernel.py:316-333; with the
+          // lazy reference maximum the largest P of a row is not the exactly representable 1.0, and an unrounded
+          // sum would leave the rounding error of the dominant key uncompensated.)
+          float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 1
+          for (int q = 0; q < 2; ++q) {
+            ptx::tmem_wait_ld();
+#pragma unroll
+            for (int x = 0; x < 32; ++x) cur[x] = nxt[x];
+            if (q == 0) {
+              DFL_TMEM_LD32_F(t_s + 32, nxt, 0);
+            } else {
+              // the whole S half is in registers: the accumulator is free for the next tile's S
+              ptx::tc_fence_before();
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive(&bars->s_free);
+            }
+#pragma unroll
+            for (int x = 0; x < 32; ++x) cur[x] = fmaf(cur[x], cscale, neg_m);
+#pragma unroll
+            for (int x = 0; x < 32; ++x) cur[x] = ptx::ex2_approx(cur[x]);
+            uint32_t packed[16];
+#pragma unroll
+            for (int x = 0; x < 32; x += 2) packed[x / 2] = Pack2<T>::pack(cur[x], cur[x + 1]);
+#pragma unroll
+            for (int x = 0; x < 16; ++x) add_pair<T>(sum[(2 * x) & 3], sum[(2 * x + 1) & 3], packed[x]);
+            // the P buffer is the A operand of the previous tile's PV until that MMA completes
+            if (q == 0 && u >= 1 && !pv_seen) {
+              ok = wwait(&bars->o_ready, c_pv & 1u, 47);
+              ++c_pv;
+              if (!ok) break;
+              ptx::tc_fence_after();
+            }
+            ptx::tmem_st16(t_p + 16 * q, packed);
+          }
+          if (!ok) break;
           l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-          TRACE(4);
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
           __syncwarp();
-          if (lane == 0) {
-            if (has_c2p) ptx::mbar_arrive(&bars->ring_release[g]);
-            if (has_p2c) ptx::mbar_arrive(&bars->pt_release[g]);
-            ptx::mbar_arrive(&bars->p_full[g]);
-          }
-          ++c_t;
-          TRACE(5);
+          if (lane == 0) ptx::mbar_arrive(&bars->p_full);
         }
         if (!ok) break;
 
-        TRACE(6);
-        // ---- merge the two streams of the row and store.  Stream g writes output columns [g*D/2, (g+1)*D/2).
-        const int my_tiles = (n - g + 1) / 2, other_tiles = n - my_tiles;
-        c_o += (uint32_t)other_tiles;
-        if (my_tiles > 0) ok = ptx::mbar_wait_inline(&bars->o_ready[g], (c_t & 1u) ^ 1u, abort_flag, status_word, 23);
-        if (ok && other_tiles > 0)
-          ok = ptx::mbar_wait_inline(&bars->o_ready[1 - g], (c_o & 1u) ^ 1u, abort_flag, status_word, 24);
-        if (!ok) break;
-        float2* xchg = xchg_base + (c_m & 1u) * (2 * BM);   // slots alternate: a stream may be one item ahead
-        xchg[g * BM + r] = make_float2(m_run, l_run);
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&bars->xbar_a);
-        ok = ptx::mbar_wait_inline(&bars->xbar_a, c_m & 1u, abort_flag, status_word, 34);
+        // ---- the item's last PV, then normalise and store this thread's half of the output columns
+        ok = wwait(&bars->o_ready, c_pv & 1u, 48);
+        ++c_pv;
         if (!ok) break;
         ptx::tc_fence_after();
-        const float2 other = xchg[(1 - g) * BM + r];
-        const float m_all = fmaxf(m_run, other.x);
-        const float m_fin = m_all == -INFINITY ? 0.0f : m_all;
-        const float a_me = my_tiles > 0 && m_run != -INFINITY ? ptx::ex2_approx((m_run - m_fin) * cscale) : 0.0f;
-        const float a_ot = other_tiles > 0 && other.x != -INFINITY ? ptx::ex2_approx((other.x - m_fin) * cscale) : 0.0f;
-        const float inv = 1.0f / (l_run * a_me + other.y * a_ot);
-        constexpr int HW = D / 2;   // output columns per thread
-        uint32_t o_me[HW], o_ot[HW];
-        if (my_tiles > 0) attn::tmem_ld_n(t_o + g * HW, o_me);
-        if (other_tiles > 0) attn::tmem_ld_n(t_o_other + g * HW, o_ot);
+        xsum[hf * BM + r] = l_run;
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(pair2);
+        ok = wwait(pair2, c_p2 & 1u, 49);
+        ++c_p2;
+        if (!ok) break;
+        const float inv = 1.0f / (l_run + xsum[(1 - hf) * BM + r]);
+        uint32_t o[OW];
+        attn::tmem_ld_n(t_o, o);
         ptx::tmem_wait_ld();
-        // Both accumulators are in registers: the PV issuer may start the next item's accumulation (it waits for the
-        // eight arrivals); the streams themselves go on without waiting for each other's stores.
+        // the accumulator is in registers: the next item's second C2P block and first PV may overwrite it
         ptx::tc_fence_before();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&bars->xbar_b);
-        float res[HW];
-#pragma unroll
-        for (int x = 0; x < HW; ++x) {
-          float v = my_tiles > 0 ? __uint_as_float(o_me[x]) * a_me : 0.0f;
-          if (other_tiles > 0) v = fmaf(__uint_as_float(o_ot[x]), a_ot, v);
-          res[x] = v * inv;
-        }
+        if (lane == 0) ptx::mbar_arrive(&bars->o_free);
         if (row_ok) {
-          T* out = reinterpret_cast<T*>(p.out) + ((long long)b * L + i) * ((long long)H * D) + (long long)h * D + g * HW;
+          T* out = reinterpret_cast<T*>(p.out) + ((long long)b * L + i) * ((long long)H * D) + (long long)h * D + hf * OW;
 #pragma unroll
-          for (int v = 0; v < HW / 8; ++v) {
+          for (int v = 0; v < OW / 8; ++v) {
             uint4 pk;
-            pk.x = Pack2<T>::pack(res[v * 8 + 0], res[v * 8 + 1]);
-            pk.y = Pack2<T>::pack(res[v * 8 + 2], res[v * 8 + 3]);
-            pk.z = Pack2<T>::pack(res[v * 8 + 4], res[v * 8 + 5]);
-            pk.w = Pack2<T>::pack(res[v * 8 + 6], res[v * 8 + 7]);
+            pk.x = Pack2<T>::pack(__uint_as_float(o[v * 8 + 0]) * inv, __uint_as_float(o[v * 8 + 1]) * inv);
+            pk.y = Pack2<T>::pack(__uint_as_float(o[v * 8 + 2]) * inv, __uint_as_float(o[v * 8 + 3]) * inv);
+            pk.z = Pack2<T>::pack(__uint_as_float(o[v * 8 + 4]) * inv, __uint_as_float(o[v * 8 + 5]) * inv);
+            pk.w = Pack2<T>::pack(__uint_as_float(o[v * 8 + 6]) * inv, __uint_as_float(o[v * 8 + 7]) * inv);
             *reinterpret_cast<uint4*>(out + v * 8) = pk;
           }
         }
-        ++c_m;
-        TRACE(7);
-        if (has_c2p) c_blk0 += (uint32_t)n + 2u;
       }
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&bars->item_empty[slot]);
     }
-  } else if (warp < kConvHiWarp0) {
-    setmaxnreg_dec();
-    converter_role();
-  } else {
-    setmaxnreg_dec();
-    if (warp < kTmaWarp) {
-      pv_role();
-    } else if (warp == kTmaWarp) {
-    // ------------------------------------------------- mask analysis + TMA producer
-    uint32_t c_q = 0, c_kv = 0, c_pk = 0, c_fq = 0;   // running counts: Q loads, K/V tiles, rel_key / rel_query blocks
+  } else if (warp < kMmaWarp) {
+    setmaxnreg_dec<kConvRegs>();
+    // -------------------------------------------------------------- converters
+    // Thread (quarter q4, lane) owns TMEM lane 32*q4 + lane of both transit accumulators:
+    //   C2P blocks: query row r of the tile; the block's 128 columns are rounded and stored to ring row r.
+    //   P2C halves: key n of the tile.  Of the 256 table rows of the tile's window, the 128 queries reach rows
+    //     n+1 .. n+128; the chunk-aligned span [8*(n/8), 8*(n/8) + 136) is stored to staging row n.
+    // Jobs are taken in the order the MMA issuer produces them.
+    const int q4 = warp & 3;
+    const int row = q4 * 32 + lane;
+    const int c_first = row >> 3;   // first chunk of the staging span (chunks are 8 table rows = 16 bytes)
+    const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
+    const uint32_t t_xp = tmem_base + lane_base + COL_XP;
+    const uint32_t t_xc = tmem_base + lane_base + COL_XC;
+    const uint32_t t_b1 = tmem_base + lane_base + COL_P;   // second block of an item: P and O columns
+    const uint32_t stg_row = ptx::smem_u32(smem + LO::offStg) + (uint32_t)(row * STG_PITCH) - (uint32_t)(c_first * 16);
+    const uint32_t ring_row = ptx::smem_u32(smem + LO::offRing) + (uint32_t)(row * RING_PITCH);
+    uint32_t c_xp = 0, c_xc = 0, c_b1 = 0, c_pt = 0;
+    uint32_t rel_seen = 0;      // phases of ring_release (one per key tile) waited for so far
+    uint32_t tiles_before = 0;  // key tiles of all earlier items
     bool ok = true;
+
+    // One C2P block: TMEM (two pieces of 64 columns) -> 16-bit -> ring block `pos` of this thread's row.  The ring
+    // position must be free: `need` key tiles in total must have been read by all softmax warps.
+    auto convert_block = [&](uint32_t t_src, uint64_t* full, uint32_t full_parity, bool frees_xc, int pos, uint32_t need) -> bool {
+      if (!wwait(full, full_parity, 18)) return false;
+      ptx::tc_fence_after();
+#pragma unroll 1
+      for (int piece = 0; piece < 2; ++piece) {
+        uint32_t r0[32], r1[32];
+        ptx::tmem_ld32(t_src + piece * 64, r0);
+        ptx::tmem_ld32(t_src + piece * 64 + 32, r1);
+        ptx::tmem_wait_ld();
+        if (piece == 1 && frees_xc) {   // the block is in registers: the accumulator is free for the next block's MMA
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&bars->xc_free);
+        }
+        if (piece == 0) {
+          while (rel_seen < need) {
+            if (!wwait(&bars->ring_release, rel_seen & 1u, 17)) return false;
+            ++rel_seen;
+          }
+        }
+        const uint32_t dst = ring_row + (uint32_t)(pos * 256 + piece * 128);
+#pragma unroll
+        for (int x = 0; x < 32; x += 2) {
+          const uint32_t w = Pack2<T>::pack(__uint_as_float(r0[x]), __uint_as_float(r0[x + 1]));
+          sts_u32(dst + 2 * x, w);
+          if (x < RING_MIRROR && pos == 0 && piece == 0) sts_u32(dst + RING_COLS * 2 + 2 * x, w);
+        }
+#pragma unroll
+        for (int x = 0; x < 32; x += 2)
+          sts_u32(dst + 64 + 2 * x, Pack2<T>::pack(__uint_as_float(r1[x]), __uint_as_float(r1[x + 1])));
+      }
+      return true;
+    };
+    // One half (128 table rows) of a tile's P2C accumulator -> staging.  half 0 also waits for the staging tile.
+    auto convert_half = [&](int half) -> bool {
+      if (!wwait(&bars->xp_full, c_xp & 1u, 19)) return false;
+      ptx::tc_fence_after();
+#pragma unroll 1
+      for (int piece = 0; piece < 2; ++piece) {
+        uint32_t r0[32], r1[32];
+        ptx::tmem_ld32(t_xp + piece * 64, r0);
+        ptx::tmem_ld32(t_xp + piece * 64 + 32, r1);
+        ptx::tmem_wait_ld();
+        if (piece == 1) {   // the half is in registers: the accumulator is free for the next half's MMA
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&bars->xp_free);
+        }
+        if (half == 0 && piece == 0) {
+          // the staging tile must have been read by all softmax warps (previous tile)
+          if (!wwait(&bars->pt_release, (c_pt & 1u) ^ 1u, 20)) return false;
+        }
+        // 8 chunks of 8 table rows; chunk c of the window goes to position c - c_first if that is in [0, 16]
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t (&src)[32] = c < 4 ? r0 : r1;
+          const int x = (c & 3) * 8;
+          const uint32_t w0 = Pack2<T>::pack(__uint_as_float(src[x + 0]), __uint_as_float(src[x + 1]));
+          const uint32_t w1 = Pack2<T>::pack(__uint_as_float(src[x + 2]), __uint_as_float(src[x + 3]));
+          const uint32_t w2 = Pack2<T>::pack(__uint_as_float(src[x + 4]), __uint_as_float(src[x + 5]));
+          const uint32_t w3 = Pack2<T>::pack(__uint_as_float(src[x + 6]), __uint_as_float(src[x + 7]));
+          const int chunk = half * 16 + piece * 8 + c;
+          if (chunk >= c_first && chunk <= c_first + (STG_CHUNKS - 1)) sts_v4(stg_row + (uint32_t)(chunk * 16), w0, w1, w2, w3);
+        }
+      }
+      ++c_xp;
+      return true;
+    };
+
     int k = 0;
     for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++k) {
-      const int slot = k & 1;
-      const int qt = it / n_bh, bh = it - qt * n_bh, b = bh / H, h = bh - b * H;
-      const int i0 = qt * BM;
-      ItemSlot* sl = &slots[slot];
-      TRACE(40);
-      ok = ptx::mbar_wait_inline(&bars->item_empty[slot], ((uint32_t)(k >> 1) & 1u) ^ 1u, abort_flag, status_word, 30);
+      const int slot = k % kItemSlots;
+      ok = wwait(&bars->item_full[slot], (uint32_t)(k / kItemSlots) & 1u, 32);
       if (!ok) break;
-      const uint32_t kb_mine = kept_bits_word(p, b, lane);
-      const TileRange range = tile_range(kb_mine, i0, L, lane);
-      const int t_begin = range.t_begin, t_end = range.t_end;
-      const bool any_kept = range.any_kept;
-      sl->kbits[lane] = kb_mine;
-      if (lane == 0) {
-        sl->t_begin = t_begin;
-        sl->t_end = t_end;
-        sl->any_kept = any_kept ? 1 : 0;
-        sl->bh = bh;
-        sl->i0 = i0;
-      }
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&bars->item_full[slot]);
-      TRACE(41);
-      if (!any_kept) continue;
-
-      if (lane == 0) {
-        const int n = t_end - t_begin;
-        const int e0 = t_begin * BN - i0 - 2 * BN + (L - 1);   // table row of block 0 (x0 = j_begin - i0 - 128)
-        auto load_pk = [&](int c) -> bool {
-          const int buf = c_pk & 1;
-          if (!ptx::mbar_wait_inline(&bars->pk_empty[buf], ((c_pk >> 1) & 1u) ^ 1u, abort_flag, status_word, 11)) return false;
-          ptx::mbar_arrive_expect_tx(&bars->pk_full[buf], (uint32_t)LO::kBlk);
-          ptx::tma_load_3d(smem + LO::offPK + buf * LO::kBlk, &tmap_fk, &bars->pk_full[buf], 0, e0 + c * BN, h);
-          ++c_pk;
-          return true;
-        };
-        auto load_fq = [&](int c) -> bool {
-          const int pos = c_fq & 3;
-          if (!ptx::mbar_wait_inline(&bars->fq_empty[pos], ((c_fq >> 2) & 1u) ^ 1u, abort_flag, status_word, 12)) return false;
-          ptx::mbar_arrive_expect_tx(&bars->fq_full[pos], (uint32_t)LO::kBlk);
-          ptx::tma_load_3d(smem + LO::offFQ + pos * LO::kBlk, &tmap_fq, &bars->fq_full[pos], 0, e0 + c * BN, h);
-          ++c_fq;
-          return true;
-        };
-        auto load_k = [&](int u) -> bool {
-          const int buf = (c_kv + u) & 1;
-          if (!ptx::mbar_wait_inline(&bars->k_empty[buf], (((c_kv + u) >> 1) & 1u) ^ 1u, abort_flag, status_word, 1)) return false;
-          ptx::mbar_arrive_expect_tx(&bars->k_full[buf], (uint32_t)LO::kBlk);
-          ptx::tma_load_3d(smem + LO::offK + buf * LO::kBlk, &tmap_k, &bars->k_full[buf], 0, (t_begin + u) * BN, bh);
-          return true;
-        };
-        auto load_v = [&](int u) -> bool {
-          const int buf = (c_kv + u) & 1;
-          if (!ptx::mbar_wait_inline(&bars->v_empty[buf], (((c_kv + u) >> 1) & 1u) ^ 1u, abort_flag, status_word, 2)) return false;
-          ptx::mbar_arrive_expect_tx(&bars->v_full[buf], (uint32_t)LO::kBlk);
-          ptx::tma_load_3d(smem + LO::offV + buf * LO::kBlk, &tmap_v, &bars->v_full[buf], 0, (t_begin + u) * BN, bh);
-          return true;
-        };
-        ok = ptx::mbar_wait_inline(&bars->q_empty, (c_q & 1u) ^ 1u, abort_flag, status_word, 3);
-        if (ok) {
-          ptx::mbar_arrive_expect_tx(&bars->q_full, (uint32_t)LO::kQ);
-          ptx::tma_load_3d(smem + LO::offQ, &tmap_q, &bars->q_full, 0, i0, bh);
-          ++c_q;
-        }
-        // Issue order: what the MMA front of a tile needs (rel_key block, K, rel_query block) first; the V tile,
-        // whose stage is released only by the PV two tiles back, trails by one tile so that waiting for it never
-        // holds back the next tile's front loads.
-        if (ok && has_c2p) ok = load_pk(0) && load_pk(1);
-        if (ok) ok = load_k(0);
-        if (ok && has_p2c) ok = load_fq(0) && load_fq(1) && load_fq(2);
-        if (ok && has_c2p) ok = load_pk(2);
-        for (int u = 1; u < n && ok; ++u) {
-          if (has_c2p) ok = load_pk(u + 2);
-          if (ok) ok = load_k(u);
-          if (ok && has_p2c) ok = load_fq(u + 2);
-          if (ok) ok = load_v(u - 1);
-        }
-        if (ok) ok = load_v(n - 1);
-        c_kv += (uint32_t)n;
-      }
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-    }
-    } else {
-    // -------------------------------------------------------------- MMA issuer
-    // One thread issues the "front" of every tile (new C2P block(s), PT, S), so its instruction count per tile bounds
-    // the tile rate: descriptors are kept as precomputed 32-bit halves (only the start-address field moves).
-    if (lane == 0) {
-      constexpr int is_bf16 = __is_same(T, __nv_bfloat16) ? 1 : 0;
-      constexpr uint32_t idesc_64 = ptx::make_idesc_f16(is_bf16, BM, BN, 0, 0);  // 128 x 64, both K-major
-      constexpr uint32_t mode = ptx::swizzle_mode_for_row_bytes(LO::kRowBytes);
-      constexpr uint32_t sbo = 8 * LO::kRowBytes;
-      constexpr int kSteps = LO::kRowBytes / 32;  // K=16 steps over d
-      // shared-memory descriptor = {lo, hi}: lo = start>>4 | (leading offset>>4) << 16, hi = stride offset>>4 |
-      // version 1 << 14 | swizzle << 29; every operand here shares hi
-      constexpr uint32_t desc_hi = ((sbo >> 4) & 0x3FFFu) | (1u << 14) | (mode << 29);
-      constexpr uint32_t kBlkUnits = (uint32_t)LO::kBlk >> 4;
-      auto desc_lo = [](uint32_t addr, uint32_t lbo) { return ((addr >> 4) & 0x3FFFu) | ((lbo >> 4) << 16); };
-      const uint32_t q_lo = desc_lo(ptx::smem_u32(smem + LO::offQ), 16);
-      const uint32_t pk_lo = desc_lo(ptx::smem_u32(smem + LO::offPK), 16);
-      const uint32_t fq_lo = desc_lo(ptx::smem_u32(smem + LO::offFQ), 16);
-      const uint32_t k_lo = desc_lo(ptx::smem_u32(smem + LO::offK), 16);
-      uint32_t c_q = 0, c_front = 0, c_pk = 0, c_fq = 0, c_pt = 0;
-      uint32_t c_s0 = 0, c_s1 = 0;   // per stream: S tiles issued
-      bool ok = true;
-
-      // D[128 x 64] = A[128 x d] * B[64 x d]^T, both operands K-major tiles in shared memory
-      auto mma_128x64 = [&](uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo) {
-#pragma unroll
-        for (int kk = 0; kk < kSteps; ++kk) {
-          if (kk == 0) umma_ss_lohi<0>(d_tmem, a_lo, b_lo, desc_hi, idesc_64);
-          else umma_ss_lohi<1>(d_tmem, a_lo + 2u * kk, b_lo + 2u * kk, desc_hi, idesc_64);
-        }
-      };
-
-      // everything tile u needs before its softmax: new C2P block(s), PT, S
-      auto front = [&](int u, int n) -> bool {
-        const int g = u & 1;
-        if (u == 0) {
-          if (!ptx::mbar_wait_inline(&bars->q_full, c_q & 1u, abort_flag, status_word, 4)) return false;
-          ++c_q;
-        }
-        if (has_c2p) {
-          const int jobs = u == 0 ? 3 : 1;
-          for (int x = 0; x < jobs; ++x, ++c_pk) {
-            const uint32_t buf = c_pk & 1u;
-            TRACE(20);
-            if (!ptx::mbar_wait_inline(&bars->pk_full[buf], (c_pk >> 1) & 1u, abort_flag, status_word, 13)) return false;
-            TRACE(21);
-            if (!ptx::mbar_wait_inline(&bars->cnew_free, (c_pk & 1u) ^ 1u, abort_flag, status_word, 14)) return false;
-            TRACE(22);
-            ptx::tc_fence_after();
-            mma_128x64(tmem_base + COL_CNEW, q_lo, pk_lo + buf * kBlkUnits);
-            ptx::umma_commit(&bars->pk_empty[buf]);
-            ptx::umma_commit(&bars->cnew_full);
+      const ItemSlot* sl = &slots[slot];
+      const int n = sl->t_end - sl->t_begin;
+      if (sl->any_kept != 0) {
+        // jobs of the item in production order: block 0 | P2C of tile 0 | block 1 | per further tile u: first half,
+        // block u + 1, second half
+        for (int u = 0; u < n && ok; ++u) {
+          if (u == 0) {
+            if (has_c2p) {
+              ok = convert_block(t_xc, &bars->xc_full, c_xc & 1u, true, 0, tiles_before);
+              ++c_xc;
+            }
+            if (ok && has_p2c) ok = convert_half(0) && convert_half(1);
+            if (ok && has_c2p) {
+              ok = convert_block(t_b1, &bars->b1_full, c_b1 & 1u, false, 1, tiles_before);
+              ++c_b1;
+            }
+          } else {
+            if (has_p2c) ok = convert_half(0);
+            if (ok && has_c2p) {
+              // block u + 1 replaces block u - 1, last read by tile u - 1
+              ok = convert_block(t_xc, &bars->xc_full, c_xc & 1u, true, (u + 1) & 1, tiles_before + (uint32_t)u);
+              ++c_xc;
+            }
+            if (ok && has_p2c) ok = convert_half(1);
           }
-        }
-        const uint32_t kb = c_front & 1u;
-        if (!ptx::mbar_wait_inline(&bars->k_full[kb], (c_front >> 1) & 1u, abort_flag, status_word, 5)) return false;
-        TRACE(23);
-        const uint32_t kt_lo = k_lo + kb * kBlkUnits;
-        if (has_p2c) {
-          // window of tile u = table blocks u, u+1, u+2 of the item, at ring positions p, p+1, p+2 (mod 4)
-          const int first = u == 0 ? 0 : 2;
-          for (int x = first; x < 3; ++x) {
-            const uint32_t blk = c_fq + (uint32_t)x;
-            if (!ptx::mbar_wait_inline(&bars->fq_full[blk & 3], (blk >> 2) & 1u, abort_flag, status_word, 15)) return false;
+          if (!ok) break;
+          __syncwarp();
+          if (lane == 0) {
+            if (has_c2p) ptx::mbar_arrive(&bars->c2p_ready);
+            if (has_p2c) ptx::mbar_arrive(&bars->pt_ready);
           }
-          TRACE(24);
-          if (!ptx::mbar_wait_inline(&bars->pt_free, (c_pt & 1u) ^ 1u, abort_flag, status_word, 16)) return false;
-          TRACE(25);
-          ptx::tc_fence_after();
-          const uint32_t pp = c_fq & 3u;
-          // 128 contiguous operand rows, then the remaining block: positions (p, p+1 | p+2), except p = 3 where
-          // the contiguous pair is blocks u+1, u+2 at positions 0, 1 and block u sits alone at position 3
-          const uint32_t a1 = pp == 3u ? 0u : pp;
-          const uint32_t a2 = pp == 3u ? 3u : (pp + 2u) & 3u;
-          mma_128x64(tmem_base + COL_PT, fq_lo + a1 * kBlkUnits, kt_lo);
-          mma_128x64(tmem_base + COL_PT + BN, fq_lo + a2 * kBlkUnits, kt_lo);
-          ptx::umma_commit(&bars->fq_empty[pp]);   // block u is not part of any later window
-          ++c_fq;
-          if (u == n - 1) {                         // the item's last two blocks
-            ptx::umma_commit(&bars->fq_empty[c_fq & 3]);
-            ++c_fq;
-            ptx::umma_commit(&bars->fq_empty[c_fq & 3]);
-            ++c_fq;
-          }
-          ptx::umma_commit(&bars->pt_full);
           ++c_pt;
         }
-        TRACE(29);
-        const uint32_t c_s = g ? c_s1 : c_s0;
-        if (!ptx::mbar_wait_inline(&bars->s_free[g], (c_s & 1u) ^ 1u, abort_flag, status_word, 6)) return false;
-        TRACE(26);
-        ptx::tc_fence_after();
-        mma_128x64(tmem_base + COL_S + g * BN, q_lo, kt_lo);
-        ptx::umma_commit(&bars->s_full[g]);
-        ptx::umma_commit(&bars->k_empty[kb]);
-        if (g) ++c_s1; else ++c_s0;
-        ++c_front;
-        if (u == n - 1) ptx::umma_commit(&bars->q_empty);
+        if (has_c2p) tiles_before += (uint32_t)n;
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&bars->item_empty[slot]);
+    }
+  } else {
+    setmaxnreg_dec<kMiscRegs>();
+    if (warp == kTmaWarp) {
+      // ------------------------------------------------- mask analysis + TMA producer
+      // Running counts of loads; stage = count % stages, phase = (count / stages) & 1.  Loads are issued in the
+      // order the MMA issuer consumes them (a stage that is still in use blocks only loads needed after its release).
+      struct LoadItem {
+        int t_begin, n, i0, bh, h;
+        bool any_kept;
+      };
+      uint32_t c_q = 0, c_k = 0, c_v = 0, c_rk = 0, c_rq = 0;
+      bool ok = true;
+
+      // Mask analysis of item number k2 (item it2), published through its slot.  Warp-collective.
+      auto analyze = [&](int k2, int it2, LoadItem& f) -> bool {
+        const int slot = k2 % kItemSlots;
+        const int qt = it2 / n_bh, bh = it2 - qt * n_bh, b = bh / H;
+        const int i0 = qt * BM;
+        ItemSlot* sl = &slots[slot];
+        if (!wwait(&bars->item_empty[slot], ((uint32_t)(k2 / kItemSlots) & 1u) ^ 1u, 30)) return false;
+        const uint32_t kb_lo = kept_bits_word(p, b, lane);
+        const uint32_t kb_hi = L > 1024 ? kept_bits_word(p, b, lane + 32) : 0u;
+        const TileRange range = tile_range(kb_lo, kb_hi, i0, L, lane);
+        sl->kbits[lane] = kb_lo;
+        sl->kbits[lane + 32] = kb_hi;
+        if (lane == 0) {
+          sl->t_begin = range.t_begin;
+          sl->t_end = range.t_end;
+          sl->any_kept = range.any_kept ? 1 : 0;
+          sl->bh = bh;
+          sl->i0 = i0;
+        }
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&bars->item_full[slot]);
+        f.t_begin = range.t_begin;
+        f.n = range.t_end - range.t_begin;
+        f.i0 = i0;
+        f.bh = bh;
+        f.h = bh - b * H;
+        f.any_kept = range.any_kept;
+        return true;
+      };
+      // table row of column 0 of block 0: pair (row r, key x) of tile u uses column 128 - r + x of blocks u, u+1
+      auto table_row0 = [&](const LoadItem& f) { return f.t_begin * BK - f.i0 - BM + (L - 1); };
+      auto load_rk = [&](const LoadItem& f, int c) -> bool {
+        const uint32_t st = c_rk % LO::kRkStages, ph = (c_rk / LO::kRkStages) & 1u;
+        if (!ptx::mbar_wait_inline(&bars->rk_empty[st], ph ^ 1u, abort_flag, fail_code, 11)) return false;
+        ptx::mbar_arrive_expect_tx(&bars->rk_full[st], (uint32_t)LO::kTile);
+        ptx::tma_load_3d(smem + LO::offRK + st * LO::kTile, &tmap_fk, &bars->rk_full[st], 0, table_row0(f) + c * BK, f.h);
+        ++c_rk;
+        return true;
+      };
+      auto load_rq = [&](const LoadItem& f, int c) -> bool {
+        const uint32_t st = c_rq & 1u, ph = (c_rq >> 1) & 1u;
+        if (!ptx::mbar_wait_inline(&bars->rq_empty[st], ph ^ 1u, abort_flag, fail_code, 12)) return false;
+        ptx::mbar_arrive_expect_tx(&bars->rq_full[st], (uint32_t)LO::kTile);
+        ptx::tma_load_3d(smem + LO::offRQ + st * LO::kTile, &tmap_fq, &bars->rq_full[st], 0, table_row0(f) + c * BK, f.h);
+        ++c_rq;
+        return true;
+      };
+      auto load_k = [&](const LoadItem& f, int u) -> bool {
+        const uint32_t st = c_k & 1u, ph = (c_k >> 1) & 1u;
+        if (!ptx::mbar_wait_inline(&bars->k_empty[st], ph ^ 1u, abort_flag, fail_code, 1)) return false;
+        ptx::mbar_arrive_expect_tx(&bars->k_full[st], (uint32_t)LO::kTile);
+        ptx::tma_load_3d(smem + LO::offK + st * LO::kTile, &tmap_k, &bars->k_full[st], 0, (f.t_begin + u) * BK, f.bh);
+        ++c_k;
+        return true;
+      };
+      auto load_v = [&](const LoadItem& f, int u) -> bool {
+        const uint32_t st = c_v % LO::kVStages, ph = (c_v / LO::kVStages) & 1u;
+        if (!ptx::mbar_wait_inline(&bars->v_empty[st], ph ^ 1u, abort_flag, fail_code, 2)) return false;
+        ptx::mbar_arrive_expect_tx(&bars->v_full[st], (uint32_t)LO::kTile);
+        ptx::tma_load_3d(smem + LO::offV + st * LO::kTile, &tmap_v, &bars->v_full[st], 0, (f.t_begin + u) * BK, f.bh);
+        ++c_v;
+        return true;
+      };
+      // what the first MMAs of an item need: Q, first rel_key block, K of the first tile, first two rel_query blocks
+      auto prologue_loads = [&](const LoadItem& f) -> bool {
+        if (!ptx::mbar_wait_inline(&bars->q_empty, (c_q & 1u) ^ 1u, abort_flag, fail_code, 3)) return false;
+        ptx::mbar_arrive_expect_tx(&bars->q_full, (uint32_t)LO::kTile);
+        ptx::tma_load_3d(smem + LO::offQ, &tmap_q, &bars->q_full, 0, f.i0, f.bh);
+        ++c_q;
+        if (has_c2p && !load_rk(f, 0)) return false;
+        if (!load_k(f, 0)) return false;
+        if (has_p2c && !(load_rq(f, 0) && load_rq(f, 1))) return false;
         return true;
       };
 
-      // The fronts run ahead of the softmax streams as far as the buffers allow, also into the next item; the PV of
-      // a tile is issued by the softmax stream that produced its P.
-      int k = 0;
-      for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++k) {
-        const int slot = k & 1;
-        ok = ptx::mbar_wait_inline(&bars->item_full[slot], (uint32_t)(k >> 1) & 1u, abort_flag, status_word, 31);
-        if (!ok) break;
-        const ItemSlot* sl = &slots[slot];
-        if (sl->any_kept != 0) {
-          const int n = sl->t_end - sl->t_begin;
-          for (int u = 0; u < n && ok; ++u) ok = front(u, n);
-        }
-        ptx::mbar_arrive(&bars->item_empty[slot]);
+      LoadItem cur{}, nxt{};
+      int it = blockIdx.x, k = 0;
+      if (it < n_items) {
+        ok = analyze(0, it, cur);
+        if (ok && cur.any_kept && lane == 0) ok = prologue_loads(cur);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       }
-    }
+      for (; it < n_items && ok; it += gridDim.x, ++k) {
+        const bool has_next = n_items - it > (int)gridDim.x;
+        // what the item needs right at its start goes out before the next item's mask is analysed
+        if (cur.any_kept && lane == 0) {
+          if (has_c2p) ok = load_rk(cur, 1);
+          if (ok && cur.n > 1) {
+            ok = load_k(cur, 1);
+            if (ok && has_c2p) ok = load_rk(cur, 2);
+            if (ok && has_p2c) ok = load_rq(cur, 2);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (ok && has_next) ok = analyze(k + 1, it + (int)gridDim.x, nxt);
+        if (!ok) break;
+        const bool next_kept = has_next && nxt.any_kept;
+        if (lane == 0) {
+          if (cur.any_kept) {
+            for (int u = 0; u < cur.n && ok; ++u) {
+              if (u + 1 < cur.n) {
+                if (u > 0) {
+                  ok = load_k(cur, u + 1);
+                  if (ok && has_c2p) ok = load_rk(cur, u + 2);
+                  if (ok && has_p2c) ok = load_rq(cur, u + 2);
+                }
+              } else if (next_kept) {
+                ok = prologue_loads(nxt);
+              }
+              if (ok) ok = load_v(cur, u);
+            }
+          } else if (next_kept) {
+            ok = prologue_loads(nxt);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        cur = nxt;
+      }
+    } else if (warp == kMmaWarp) {
+      // -------------------------------------------------------------- MMA issuer
+      // One thread issues every MMA; descriptors are kept as precomputed 32-bit halves (only the start-address
+      // field moves).  Order per key tile u (steady state): the next tile's first P2C half, new C2P block and second
+      // P2C half while the softmax threads work on tile u, the next tile's S as soon as they have read S(u), then
+      // PV(u) as soon as P(u) is stored.  In the item's last tile the place of the next tile's MMAs is taken by the
+      // first MMAs of the next item.
+      if (lane == 0) {
+        constexpr int is_bf16 = __is_same(T, __nv_bfloat16) ? 1 : 0;
+        constexpr uint32_t idesc_nn = ptx::make_idesc_f16(is_bf16, BM, 128, 0, 0);   // 128 x 128, both K-major
+        constexpr uint32_t idesc_pv = ptx::make_idesc_f16(is_bf16, BM, D, 0, 1);     // 128 x D, V is MN-major
+        constexpr uint32_t mode = ptx::swizzle_mode_for_row_bytes(LO::kRowBytes);
+        constexpr uint32_t sbo = 8 * LO::kRowBytes;
+        constexpr int kSteps = LO::kRowBytes / 32;   // K=16 steps over d
+        // shared-memory descriptor = {lo, hi}: lo = start>>4 | (leading offset>>4) << 16, hi = stride offset>>4 |
+        // version 1 << 14 | swizzle << 29; every operand here shares hi
+        constexpr uint32_t desc_hi = ((sbo >> 4) & 0x3FFFu) | (1u << 14) | (mode << 29);
+        constexpr uint32_t kTileUnits = (uint32_t)LO::kTile >> 4;
+        constexpr uint32_t kPvStepUnits = (16u * LO::kRowBytes) >> 4;   // 16 keys further down the V tile
+        auto desc_lo = [](uint32_t addr, uint32_t lbo) { return ((addr >> 4) & 0x3FFFu) | ((lbo >> 4) << 16); };
+        const uint32_t q_lo = desc_lo(ptx::smem_u32(smem + LO::offQ), 16);
+        const uint32_t k_lo = desc_lo(ptx::smem_u32(smem + LO::offK), 16);
+        const uint32_t rk_lo = desc_lo(ptx::smem_u32(smem + LO::offRK), 16);
+        const uint32_t rq_lo = desc_lo(ptx::smem_u32(smem + LO::offRQ), 16);
+        const uint32_t v_lo = ((ptx::smem_u32(smem + LO::offV) >> 4) & 0x3FFFu) | (kTileUnits << 16);
+        uint32_t c_q = 0, c_k = 0, c_v = 0, c_rk = 0;   // loads consumed (stage / phase as in the loader)
+        uint32_t c_s = 0, c_xc = 0, c_xp = 0, c_p = 0;  // S tiles, C2P blocks through XC, P2C halves, PVs issued
+        uint32_t rq_alloc = 0;                          // rel_query blocks handed to items so far
+        bool ok = true;
+
+        // D[128 x 128] = A[128 x d] * B[128 x d]^T, both operands K-major tiles in shared memory
+        auto mma_nn = [&](uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo) {
+#pragma unroll
+          for (int kk = 0; kk < kSteps; ++kk) {
+            if (kk == 0) umma_ss_lohi<0>(d_tmem, a_lo, b_lo, desc_hi, idesc_nn);
+            else umma_ss_lohi<1>(d_tmem, a_lo + 2u * kk, b_lo + 2u * kk, desc_hi, idesc_nn);
+          }
+        };
+        auto wait1 = [&](uint64_t* bar, uint32_t parity, int code) -> bool {
+          return ptx::mbar_wait_inline(bar, parity, abort_flag, fail_code, code);
+        };
+        // new C2P block = Q . rel_key block^T, into the block accumulator, or (second block of an item) into the
+        // P and O columns, which the caller has made sure are idle
+        auto issue_c = [&](bool second_block) -> bool {
+          const uint32_t st = c_rk % LO::kRkStages, ph = (c_rk / LO::kRkStages) & 1u;
+          if (!wait1(&bars->rk_full[st], ph, 13)) return false;
+          if (!second_block && !wait1(&bars->xc_free, (c_xc & 1u) ^ 1u, 14)) return false;
+          ptx::tc_fence_after();
+          mma_nn(tmem_base + (second_block ? COL_P : COL_XC), q_lo, rk_lo + st * kTileUnits);
+          ptx::umma_commit(&bars->rk_empty[st]);
+          ptx::umma_commit(second_block ? &bars->b1_full : &bars->xc_full);
+          ++c_rk;
+          if (!second_block) ++c_xc;
+          return true;
+        };
+        // S = Q . K^T of the tile whose K is in stage kst
+        auto issue_s = [&](uint32_t kst) -> bool {
+          if (!wait1(&bars->s_free, (c_s & 1u) ^ 1u, 6)) return false;
+          ptx::tc_fence_after();
+          mma_nn(tmem_base + COL_S, q_lo, k_lo + kst * kTileUnits);
+          ptx::umma_commit(&bars->s_full);
+          ++c_s;
+          return true;
+        };
+        // one half of the P2C accumulator: XP[n, m] = K . rel_query block^T; `first` = first use of the table block
+        // (wait for its load), `last` = last use (release its stage)
+        auto issue_pt = [&](uint32_t kst, uint32_t blk, bool first, bool last) -> bool {
+          const uint32_t st = blk & 1u, ph = (blk >> 1) & 1u;
+          if (first && !wait1(&bars->rq_full[st], ph, 15)) return false;
+          if (!wait1(&bars->xp_free, (c_xp & 1u) ^ 1u, 16)) return false;
+          ptx::tc_fence_after();
+          mma_nn(tmem_base + COL_XP, k_lo + kst * kTileUnits, rq_lo + st * kTileUnits);
+          if (last) ptx::umma_commit(&bars->rq_empty[st]);
+          ptx::umma_commit(&bars->xp_full);
+          ++c_xp;
+          return true;
+        };
+        // The first MMAs of an item with n key tiles: first C2P block, both P2C halves of tile 0, S(0).  rq0 receives
+        // the number of the item's first rel_query block (tile u uses blocks rq0 + u and rq0 + u + 1).
+        auto item_head = [&](int n, uint32_t& rq0) -> bool {
+          if (!wait1(&bars->q_full, c_q & 1u, 4)) return false;
+          ++c_q;
+          if (has_c2p && !issue_c(false)) return false;
+          const uint32_t kst = c_k & 1u;
+          if (!wait1(&bars->k_full[kst], (c_k >> 1) & 1u, 5)) return false;
+          rq0 = rq_alloc;
+          if (has_p2c) {
+            if (!(issue_pt(kst, rq0, true, true) && issue_pt(kst, rq0 + 1u, true, n == 1))) return false;
+            rq_alloc += (uint32_t)n + 1u;
+          }
+          if (!issue_s(kst)) return false;
+          ptx::umma_commit(&bars->k_empty[kst]);
+          ++c_k;
+          return true;
+        };
+        struct ItemInfo {
+          bool any_kept;
+          int n;
+        };
+        auto get_item = [&](int k2, ItemInfo& f) -> bool {
+          const int slot = k2 % kItemSlots;
+          if (!wait1(&bars->item_full[slot], (uint32_t)(k2 / kItemSlots) & 1u, 31)) return false;
+          f.any_kept = slots[slot].any_kept != 0;
+          f.n = slots[slot].t_end - slots[slot].t_begin;
+          return true;
+        };
+
+        ItemInfo cur{false, 0}, nxt{false, 0};
+        uint32_t cur_rq = 0, nxt_rq = 0;
+        int it = blockIdx.x, k = 0;
+        if (it < n_items) {
+          ok = get_item(0, cur);
+          if (ok && cur.any_kept) ok = item_head(cur.n, cur_rq);
+        }
+        for (; it < n_items && ok; it += gridDim.x, ++k) {
+          const bool has_next = n_items - it > (int)gridDim.x;
+          // the output accumulator of the previous item has been read out (every item completes a phase of o_free)
+          if (k > 0) ok = wait1(&bars->o_free, (uint32_t)(k - 1) & 1u, 38);
+          if (!ok) break;
+          if (cur.any_kept) {
+            const int n = cur.n;
+            if (has_c2p) ok = issue_c(true);
+            if (ok && n == 1) ptx::umma_commit(&bars->q_empty);
+            for (int u = 0; u < n && ok; ++u) {
+              if (u + 1 < n) {
+                // ---- front of tile u + 1
+                const uint32_t kst = c_k & 1u;
+                ok = wait1(&bars->k_full[kst], (c_k >> 1) & 1u, 5);
+                if (ok && has_p2c) ok = issue_pt(kst, cur_rq + (uint32_t)(u + 1), false, true);
+                if (ok && has_c2p) ok = issue_c(false);
+                if (ok && has_p2c) ok = issue_pt(kst, cur_rq + (uint32_t)(u + 2), true, u + 2 == n);
+                if (ok) ok = issue_s(kst);   // waits until the softmax threads have read the current tile's S
+                if (!ok) break;
+                ptx::umma_commit(&bars->k_empty[kst]);
+                ++c_k;
+                if (u + 2 == n) ptx::umma_commit(&bars->q_empty);   // S(n-1) and the last C2P block are issued
+              } else if (has_next) {
+                // The next item's slot is read only now: the loader publishes it after loads whose stages this
+                // thread's earlier MMAs of the current item release.
+                ok = get_item(k + 1, nxt);
+                if (ok && nxt.any_kept) ok = item_head(nxt.n, nxt_rq);
+                if (!ok) break;
+              }
+              // ---- PV(u): O (+)= P . V
+              const uint32_t vst = c_v % LO::kVStages, vph = (c_v / LO::kVStages) & 1u;
+              ok = wait1(&bars->p_full, c_p & 1u, 7) && wait1(&bars->v_full[vst], vph, 8);
+              if (!ok) break;
+              ptx::tc_fence_after();
+              const uint32_t vt_lo = v_lo + vst * kTileUnits;
+#pragma unroll
+              for (int kk = 0; kk < BK / 16; ++kk)
+                umma_ts_lohi(tmem_base + COL_O, tmem_base + COL_P + kk * 8, vt_lo + kk * kPvStepUnits, desc_hi, idesc_pv,
+                             (u > 0 || kk > 0) ? 1u : 0u);
+              ptx::umma_commit(&bars->v_empty[vst]);
+              ptx::umma_commit(&bars->o_ready);
+              ++c_v;
+              ++c_p;
+            }
+          } else if (has_next) {
+            ok = get_item(k + 1, nxt);
+            if (ok && nxt.any_kept) ok = item_head(nxt.n, nxt_rq);
+          }
+          if (!ok) break;
+          ptx::mbar_arrive(&bars->item_empty[k % kItemSlots]);
+          cur = nxt;
+          cur_rq = nxt_rq;
+        }
+      }
     }
   }
 
+  if (fail_code != 0 && status_word != nullptr) atomicCAS(status_word, 0, fail_code);
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == kMmaWarp) ptx::tmem_dealloc(tmem_base, kTmemCols);
@@ -948,31 +1121,36 @@ int launch_rel_typed(const DflAttnRelParams& p, cudaStream_t stream) {
   const uint64_t row = (uint64_t)D * sizeof(T), seq = (uint64_t)L * row, table = (uint64_t)R * row;
   CUtensorMap tq, tk, tv, tfk, tfq;
   int rc = encode_tensor_map_3d(&tq, p.q, D, L, BH, row, seq, D, BM, LO::kRowBytes);
-  if (rc == DFL_OK) rc = encode_tensor_map_3d(&tk, p.k, D, L, BH, row, seq, D, BN, LO::kRowBytes);
-  if (rc == DFL_OK) rc = encode_tensor_map_3d(&tv, p.v, D, L, BH, row, seq, D, BN, LO::kRowBytes);
+  if (rc == DFL_OK) rc = encode_tensor_map_3d(&tk, p.k, D, L, BH, row, seq, D, BK, LO::kRowBytes);
+  if (rc == DFL_OK) rc = encode_tensor_map_3d(&tv, p.v, D, L, BH, row, seq, D, BK, LO::kRowBytes);
   // a disabled term reuses the other table's map; it is never dereferenced
   const void* fk = p.rel_key ? p.rel_key : p.rel_query;
   const void* fq = p.rel_query ? p.rel_query : p.rel_key;
-  if (rc == DFL_OK) rc = encode_tensor_map_3d(&tfk, fk, D, R, p.heads, row, table, D, BN, LO::kRowBytes);
-  if (rc == DFL_OK) rc = encode_tensor_map_3d(&tfq, fq, D, R, p.heads, row, table, D, BN, LO::kRowBytes);
+  if (rc == DFL_OK) rc = encode_tensor_map_3d(&tfk, fk, D, R, p.heads, row, table, D, BK, LO::kRowBytes);
+  if (rc == DFL_OK) rc = encode_tensor_map_3d(&tfq, fq, D, R, p.heads, row, table, D, BK, LO::kRowBytes);
   if (rc != DFL_OK) return rc;
 
   auto kernel = attention_rel_kernel<T, D>;
-  // one-time configuration per device (the opt-in to large dynamic shared memory is a per-device attribute)
-  constexpr int kMaxDevices = 64;
+  // One-time configuration per device and kernel instance (the opt-in to large dynamic shared memory is a
+  // per-device attribute), guarded against concurrent first calls from several host threads.
+  static std::mutex config_mutex;
   static int sm_counts[kMaxDevices] = {0};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) return fail(DFL_ERR_LAUNCH, "current device: %s", cudaGetErrorString(e));
-  if (sm_counts[dev] == 0) {
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LO::total);
-    if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "attention_rel smem opt-in: %s", cudaGetErrorString(e));
-    int count = 0;
-    e = cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess || count < 1) return fail(DFL_ERR_LAUNCH, "SM count: %s", cudaGetErrorString(e));
-    sm_counts[dev] = count;
+  int sm_count = 0;
+  {
+    std::lock_guard<std::mutex> lock(config_mutex);
+    if (sm_counts[dev] == 0) {
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LO::total);
+      if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "attention_rel smem opt-in: %s", cudaGetErrorString(e));
+      int count = 0;
+      e = cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+      if (e != cudaSuccess || count < 1) return fail(DFL_ERR_LAUNCH, "SM count: %s", cudaGetErrorString(e));
+      sm_counts[dev] = count;
+    }
+    sm_count = sm_counts[dev];
   }
-  const int sm_count = sm_counts[dev];
   int* status_word = p.status;
   if (!status_word) {
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status_word), g_attn_rel_status);
@@ -1015,15 +1193,3 @@ int launch_expand_rel_tables(const void* pos, const int32_t* lut, void* rel, int
 }
 
 }  // namespace dfl
-
-#ifdef DFL_TRACE
-extern "C" int dfl_debug_read_trace_rel(long long* host_buf, int clear) {
-  cudaDeviceSynchronize();
-  cudaError_t e = cudaMemcpyFromSymbol(host_buf, dfl::g_trace, sizeof(long long) * 16 * 512);
-  if (clear) {
-    static long long zeros[16 * 512] = {0};
-    cudaMemcpyToSymbol(dfl::g_trace, zeros, sizeof(zeros));
-  }
-  return (int)e;
-}
-#endif

@@ -34,6 +34,9 @@ inline int check_launch(const char* what) {
   return DFL_OK;
 }
 
+// Launchers keep their one-time configuration (shared-memory opt-in, SM count, symbol addresses) per device.
+constexpr int kMaxDevices = 64;
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline size_t dtype_size(int dtype) { return dtype == DFL_F32 ? 4 : 2; }

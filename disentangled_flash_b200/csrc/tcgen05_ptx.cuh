@@ -79,24 +79,29 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 // Fully inlined bounded wait, for kernels that change their register budget with setmaxnreg (such kernels
-// cannot contain calls to separately compiled device functions).
-__device__ __forceinline__ bool mbar_wait_inline(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* gstatus,
+// cannot contain calls to separately compiled device functions).  It is inlined at every wait of those kernels, and
+// they are sensitive to instruction-cache footprint, so it is kept small: the clock (low 32 bits of the nanosecond
+// timer, enough for a limit of two seconds) and the CTA's abort flag are looked at once per 1024 failed polls, and
+// the code of the wait that gave up is left in a register of the caller instead of being written from here.
+__device__ __forceinline__ uint32_t globaltimer_lo() {
+  uint32_t t;
+  asm volatile("mov.u32 %0, %%globaltimer_lo;" : "=r"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_wait_inline(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int& fail_code,
                                                  int code) {
-  unsigned long long t0 = 0;
-#pragma unroll 1
-  for (uint32_t it = 0;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 255u) == 255u) {
-      if (*abort_flag) return false;
-      const unsigned long long now = globaltimer_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) {
-        *abort_flag = 1;
-        if (gstatus) atomicCAS(gstatus, 0, code);   // the first wait that gave up is the informative one
-        return false;
-      }
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint32_t t0 = globaltimer_lo();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 1023u) != 0) continue;
+    if (*abort_flag || globaltimer_lo() - t0 > (uint32_t)kWaitLimitNs) {
+      *abort_flag = 1;     // every other wait of the CTA gives up at its next look
+      fail_code = code;    // reported by the caller once, when it leaves its role
+      return false;
     }
   }
+  return true;
 }
 
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA / tcgen05)

@@ -70,7 +70,7 @@ def test_expanded_tables_are_row_copies(dtype_name, d):
         assert torch.equal(rel_key.cpu(), want), f"L={length} buckets={buckets}"
 
 
-CORE_LENGTHS = (1, 2, 31, 32, 33, 63, 64, 65, 127, 128, 129, 255, 256, 257, 511, 512, 513, 1024)
+CORE_LENGTHS = (1, 2, 31, 32, 33, 63, 64, 65, 127, 128, 129, 255, 256, 257, 383, 384, 385, 511, 512, 513, 1024, 1100, 2048)
 
 
 @pytest.mark.parametrize("dtype_name", sorted(DTYPES))
@@ -136,7 +136,8 @@ def test_rel_kernel_padded_rows_uniform_deterministic_and_unsupported():
     assert not c.attention_rel_supported(torch.float16, 64, 128, True, True)
     assert not c.attention_rel_supported(torch.float32, 64, 64, True, True)
     assert not c.attention_rel_supported(torch.float16, 384, 64, False, False)
-    assert not c.attention_rel_supported(torch.float16, 2048, 64, True, True)
+    assert c.attention_rel_supported(torch.float16, 2048, 64, True, True)
+    assert not c.attention_rel_supported(torch.float16, 2049, 64, True, True)
     assert c.attention_rel_supported(torch.bfloat16, 1024, 32, False, True)
     with pytest.raises(c.DflError, match="not covered"):
         rel = torch.zeros(1, 127, 128, dtype=torch.float16, device=dev)
