@@ -32,6 +32,7 @@ import torch
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
+sys.path.insert(1, str(ROOT / "tests"))   # the HF-named module tree the encoder is built from (tests/hf_modules.py)
 
 WORKLOAD = dict(name="deberta-v3-base-encoder", layers=12, hidden=768, heads=12, head_dim=64, ffn=3072,
                 conv=3, batch=32, seq_len=512, min_len=256, vocab=128100, dtype="fp16")
@@ -129,7 +130,16 @@ class ClockSampler:
 
 
 class LaunchObserver:
-    """Counts C-ABI kernel launches; brackets the attention kernel with CUDA events on its stream."""
+    """Counts kernel launches of the library and times its attention kernel.
+
+    The benchmark wraps the binding's launch functions (nothing in the library knows about it): every call
+    adds the number of kernels it launches, and the fused attention calls are bracketed with CUDA events
+    recorded on the launching stream.
+    """
+
+    KERNELS = {"linear_heads": "dfl_qkv_proj", "pos_scores": "dfl_pos_scores", "attention_fwd": "dfl_attention_fwd",
+               "attention_rel_fwd": "dfl_attention_rel_fwd", "attention_fwd_static": "dfl_attention_fwd_static"}
+    TIMED = ("dfl_attention_fwd", "dfl_attention_rel_fwd")
 
     def __init__(self):
         self.enabled = False
@@ -137,32 +147,34 @@ class LaunchObserver:
         self.events = []
         self.kernel_name = None
 
-    def __call__(self, name: str, n_kernels: int):
-        if not self.enabled:
-            return None
-        self.launches += n_kernels
-        if name not in ("dfl_attention_fwd", "dfl_attention_rel_fwd"):
-            return None
-        self.kernel_name = name
-        observer = self
+    def install(self, binding):
+        for attr, name in self.KERNELS.items():
+            setattr(binding, attr, self._wrap(getattr(binding, attr), name))
 
-        class Bracket:
-            def __enter__(self):
-                self.start = torch.cuda.Event(enable_timing=True)
-                self.end = torch.cuda.Event(enable_timing=True)
-                self.start.record()
+    def _wrap(self, fn, name):
+        def call(*args, **kwargs):
+            if not self.enabled:
+                return fn(*args, **kwargs)
+            if name == "dfl_pos_scores":   # one GEMM per enabled term (pos_key, pos_query)
+                self.launches += int(args[2] is not None) + int(args[3] is not None)
+            else:
+                self.launches += 3 if name == "dfl_attention_fwd_static" else 1
+            if name not in self.TIMED:
+                return fn(*args, **kwargs)
+            self.kernel_name = name
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            out = fn(*args, **kwargs)
+            end.record()
+            self.events.append((start, end))
+            return out
 
-            def __exit__(self, *exc):
-                self.end.record()
-                observer.events.append((self.start, self.end))
-                return False
-
-        return Bracket()
+        return call
 
 
 # ----------------------------------------------------------------------------- CPU arm
 def build_cpu_encoder(layers: int, seed: int = 17):
-    from disentangled_flash_b200 import hf_modules
+    import hf_modules
 
     cfg = make_config(layers)
     backbone = hf_modules.Backbone(cfg, vocab_size=8).eval()  # the table is applied outside
@@ -273,7 +285,8 @@ def run_gpu_arm(args) -> None:
     import torch.distributed as dist
 
     import disentangled_flash_b200 as df
-    from disentangled_flash_b200 import _cabi, hf_modules, sharding
+    import hf_modules
+    from disentangled_flash_b200 import _cabi, sharding
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -301,7 +314,7 @@ def run_gpu_arm(args) -> None:
     out_host = torch.empty_like(host_hidden[0]).pin_memory()
 
     observer = LaunchObserver()
-    _cabi.set_launch_observer(observer)
+    observer.install(_cabi)
 
     def step_resident(i):
         hidden, mask = dev_batches[i % len(dev_batches)]

@@ -10,7 +10,7 @@ fails loudly.
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_uint32, c_void_p
 from pathlib import Path
 
 import torch
@@ -34,6 +34,8 @@ EXPORTED_SYMBOLS = (
     "dfl_version",
     "dfl_status_string",
     "dfl_last_error",
+    "dfl_check_status",
+    "dfl_selftest_bounded_wait",
     "dfl_build_position_lut",
     "dfl_qkv_proj",
     "dfl_gather_slots",
@@ -51,7 +53,7 @@ class DflLinearParams(Structure):
     _fields_ = [
         ("x", c_void_p), ("w", c_void_p), ("bias", c_void_p), ("out", c_void_p * 3),
         ("M", c_int32), ("K", c_int32), ("n_out", c_int32), ("heads", c_int32), ("head_dim", c_int32),
-        ("rows_per_seq", c_int32), ("dtype", c_int32), ("algo", c_int32),
+        ("rows_per_seq", c_int32), ("dtype", c_int32), ("algo", c_int32), ("status", c_void_p),
     ]
 
 
@@ -60,7 +62,7 @@ class DflPosScoreParams(Structure):
         ("q", c_void_p), ("k", c_void_p), ("pos_key", c_void_p), ("pos_query", c_void_p),
         ("c2p", c_void_p), ("p2c", c_void_p),
         ("batch", c_int32), ("heads", c_int32), ("seq_len", c_int32), ("head_dim", c_int32),
-        ("n_active", c_int32), ("ld_slots", c_int32), ("dtype", c_int32), ("algo", c_int32),
+        ("n_active", c_int32), ("ld_slots", c_int32), ("dtype", c_int32), ("algo", c_int32), ("status", c_void_p),
     ]
 
 
@@ -103,31 +105,6 @@ class DflError(RuntimeError):
 
 _lib = None
 
-# Optional launch observer: ``callback(name, n_kernels) -> context manager or None``.
-# Benchmarks install one to count launches and to bracket a kernel with CUDA
-# events on the launching stream; it is never set in normal operation.
-_launch_observer = None
-
-
-def set_launch_observer(callback) -> None:
-    global _launch_observer
-    _launch_observer = callback
-
-
-class _NullContext:
-    def __enter__(self):
-        return None
-
-    def __exit__(self, *exc):
-        return False
-
-
-def _observe(name: str, n_kernels: int):
-    if _launch_observer is None:
-        return _NullContext()
-    return _launch_observer(name, n_kernels) or _NullContext()
-
-
 def load_library() -> ctypes.CDLL:
     """Load the shared library once; raise if it has not been built."""
 
@@ -144,6 +121,10 @@ def load_library() -> ctypes.CDLL:
     lib.dfl_status_string.restype = c_char_p
     lib.dfl_status_string.argtypes = [c_int]
     lib.dfl_last_error.restype = c_char_p
+    lib.dfl_check_status.restype = c_int
+    lib.dfl_check_status.argtypes = [c_void_p, c_void_p]
+    lib.dfl_selftest_bounded_wait.restype = c_int
+    lib.dfl_selftest_bounded_wait.argtypes = [c_void_p, c_uint32, c_void_p]
     lib.dfl_build_position_lut.restype = c_int
     lib.dfl_build_position_lut.argtypes = [c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.dfl_qkv_proj.restype = c_int
@@ -175,6 +156,35 @@ def _check(status: int, where: str) -> None:
     if status in (DFL_ERR_BAD_ARG, DFL_ERR_ALIGNMENT, DFL_ERR_TOO_LARGE):
         raise ValueError(f"{where}: {detail} (status {status})")
     raise DflError(status, where, detail)
+
+
+def new_status_word(device: torch.device | str) -> torch.Tensor:
+    """A zeroed device int32 to pass as ``status=`` to the kernel wrappers (see ``check_status``)."""
+
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def check_status(status: torch.Tensor) -> None:
+    """Read a status word back (synchronises the current stream); raise if a bounded device-side wait expired.
+
+    Mirrors ``dfl_check_status``: the word is cleared when it was non-zero, and the outputs of the calls made
+    with it since the previous check are not valid.  Meant for the end of a batch, not for the hot path.
+    """
+
+    lib = load_library()
+    if status.dtype != torch.int32 or status.numel() != 1 or status.device.type != "cuda":
+        raise ValueError("status must be a CUDA int32 tensor with one element")
+    with torch.cuda.device(status.device):
+        _check(lib.dfl_check_status(status.data_ptr(), _stream(status.device)), "dfl_check_status")
+
+
+def selftest_bounded_wait(status: torch.Tensor, limit_us: int) -> None:
+    """Launch the diagnostic kernel whose only wait can never complete (``dfl_selftest_bounded_wait``)."""
+
+    lib = load_library()
+    with torch.cuda.device(status.device):
+        _check(lib.dfl_selftest_bounded_wait(status.data_ptr(), int(limit_us), _stream(status.device)),
+               "dfl_selftest_bounded_wait")
 
 
 def dtype_code(dtype: torch.dtype) -> int:
@@ -220,7 +230,8 @@ def build_position_lut(seq_len: int, position_buckets: int, max_relative_positio
 
 
 def linear_heads(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, *, n_out: int, heads: int,
-                 head_dim: int, rows_per_seq: int, algo: int = ALGO_AUTO) -> tuple[torch.Tensor, ...]:
+                 head_dim: int, rows_per_seq: int, algo: int = ALGO_AUTO,
+                 status: torch.Tensor | None = None) -> tuple[torch.Tensor, ...]:
     """``x[M,K] @ weight[N,K]^T + bias`` written as ``n_out`` tensors ``[M/rows, heads, rows, head_dim]``."""
 
     lib = load_library()
@@ -237,8 +248,8 @@ def linear_heads(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | Non
     for i, o in enumerate(outs):
         p.out[i] = o.data_ptr()
     p.M, p.K, p.n_out, p.heads, p.head_dim, p.rows_per_seq = m, k, n_out, heads, head_dim, rows_per_seq
-    p.dtype, p.algo = dtype_code(x.dtype), algo
-    with torch.cuda.device(x.device), _observe("dfl_qkv_proj", 1):
+    p.dtype, p.algo, p.status = dtype_code(x.dtype), algo, _ptr(status)
+    with torch.cuda.device(x.device):
         _check(lib.dfl_qkv_proj(ctypes.byref(p), _stream(x.device)), "dfl_qkv_proj")
     return outs
 
@@ -264,7 +275,7 @@ def padded_slots(n_active: int) -> int:
 
 
 def pos_scores(q: torch.Tensor | None, k: torch.Tensor | None, pos_key: torch.Tensor | None,
-               pos_query: torch.Tensor | None, *, algo: int = ALGO_AUTO):
+               pos_query: torch.Tensor | None, *, algo: int = ALGO_AUTO, status: torch.Tensor | None = None):
     """C2P / P2C score GEMMs over the active slots; returns ``(c2p, p2c, ld_slots)``."""
 
     lib = load_library()
@@ -279,7 +290,8 @@ def pos_scores(q: torch.Tensor | None, k: torch.Tensor | None, pos_key: torch.Te
     p.pos_key, p.pos_query, p.c2p, p.p2c = _ptr(pos_key), _ptr(pos_query), _ptr(c2p), _ptr(p2c)
     p.batch, p.heads, p.seq_len, p.head_dim = bsz, heads, length, d
     p.n_active, p.ld_slots, p.dtype, p.algo = n_active, ld, dtype_code(ref.dtype), algo
-    with torch.cuda.device(ref.device), _observe("dfl_pos_scores", int(c2p is not None) + int(p2c is not None)):
+    p.status = _ptr(status)
+    with torch.cuda.device(ref.device):
         _check(lib.dfl_pos_scores(ctypes.byref(p), _stream(ref.device)), "dfl_pos_scores")
     return c2p, p2c, ld
 
@@ -302,7 +314,7 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, c2p: torch.
     p.batch, p.heads, p.seq_len, p.head_dim = bsz, heads, length, d
     p.ld_slots, p.mask_elem_size, p.scale = ld_slots, mask.element_size(), scale
     p.dtype, p.algo = dtype_code(q.dtype), algo
-    with torch.cuda.device(q.device), _observe("dfl_attention_fwd", 1):
+    with torch.cuda.device(q.device):
         _check(lib.dfl_attention_fwd(ctypes.byref(p), _stream(q.device)), "dfl_attention_fwd")
     return out
 
@@ -341,7 +353,7 @@ def attention_fwd_static(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_
     for name, t in (("q", q), ("k", k), ("v", v), ("mask", mask), ("out", out)):
         _require_cuda_contiguous(name, t)
     p = _tables_params(q, k, v, pos_key, pos_query, lut, mask, scale, out, algo)
-    with torch.cuda.device(q.device), _observe("dfl_attention_fwd_static", 3):
+    with torch.cuda.device(q.device):
         _check(lib.dfl_attention_fwd_static(ctypes.byref(p), _stream(q.device)), "dfl_attention_fwd_static")
     return out
 
@@ -356,7 +368,7 @@ def expand_rel_tables(pos: torch.Tensor, lut: torch.Tensor, seq_len: int) -> tor
         raise ValueError("lut must be int32 [2L-1]")
     heads, n_active, d = pos.shape
     rel = torch.empty(heads, 2 * seq_len - 1, d, dtype=pos.dtype, device=pos.device)
-    with torch.cuda.device(pos.device), _observe("dfl_expand_rel_tables", 1):
+    with torch.cuda.device(pos.device):
         _check(lib.dfl_expand_rel_tables(pos.data_ptr(), lut.data_ptr(), rel.data_ptr(), heads, n_active, seq_len, d,
                                          dtype_code(pos.dtype), _stream(pos.device)), "dfl_expand_rel_tables")
     return rel
@@ -398,6 +410,6 @@ def attention_rel_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rel_key
     p.mask, p.out, p.status = mask.data_ptr(), out.data_ptr(), _ptr(status)
     p.batch, p.heads, p.seq_len, p.head_dim = bsz, heads, length, d
     p.mask_elem_size, p.scale, p.dtype, p.algo = mask.element_size(), scale, dtype_code(q.dtype), ALGO_AUTO
-    with torch.cuda.device(q.device), _observe("dfl_attention_rel_fwd", 1):
+    with torch.cuda.device(q.device):
         _check(lib.dfl_attention_rel_fwd(ctypes.byref(p), _stream(q.device)), "dfl_attention_rel_fwd")
     return out

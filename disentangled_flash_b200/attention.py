@@ -13,7 +13,7 @@ issues ``dfl_qkv_proj`` (fused QKV projection, written head-major
 ``[B,H,L,d]``) followed by
 
 * ``dfl_attention_rel_fwd`` where it applies (FP16/BF16, head dim 32/64,
-  length up to 1024): one persistent kernel that computes the C2P/P2C scores
+  length up to 2048): one persistent kernel that computes the C2P/P2C scores
   on the tensor cores from the plan's relative-distance tables and consumes
   them in place (QK^T + relative gathers + mask + softmax + PV), or otherwise
 * ``dfl_pos_scores`` (the two score GEMMs) and ``dfl_attention_fwd`` (the
@@ -62,7 +62,7 @@ class B200PreparedPositionPlan(NamedTuple):
 # dfl_qkv_proj, then dfl_attention_rel_fwd where the plan carries relative-distance
 # tables, else dfl_pos_scores + dfl_attention_fwd.
 # --------------------------------------------------------------------------
-@torch.library.custom_op("disentangled_flash_b200::attention_forward", mutates_args=(), device_types="cuda")
+@torch.library.custom_op("disentangled_flash_b200::attention_forward", mutates_args=("status",), device_types="cuda")
 def _attention_forward_op(
     hidden_states: torch.Tensor,
     attention_mask: torch.Tensor,
@@ -77,26 +77,27 @@ def _attention_forward_op(
     head_dim: int,
     scale: float,
     algo: int,
+    status: Optional[torch.Tensor],
 ) -> torch.Tensor:
     length = hidden_states.shape[1]
     query, key, value = _cabi.linear_heads(
         hidden_states, qkv_weight, qkv_bias, n_out=3, heads=num_heads, head_dim=head_dim, rows_per_seq=length,
-        algo=algo,
+        algo=algo, status=status,
     )
     if rel_key is not None or rel_query is not None:
         # relative scores are produced inside the attention kernel: no [B,H,L,A] tensor in memory
-        return _cabi.attention_rel_fwd(query, key, value, rel_key, rel_query, attention_mask, scale)
+        return _cabi.attention_rel_fwd(query, key, value, rel_key, rel_query, attention_mask, scale, status=status)
     c2p = p2c = None
     ld_slots = 0
     if pos_key is not None or pos_query is not None:
-        c2p, p2c, ld_slots = _cabi.pos_scores(query, key, pos_key, pos_query, algo=algo)
+        c2p, p2c, ld_slots = _cabi.pos_scores(query, key, pos_key, pos_query, algo=algo, status=status)
     return _cabi.attention_fwd(query, key, value, c2p, p2c, delta_to_local, attention_mask, scale,
-                               ld_slots=ld_slots, algo=algo)
+                               ld_slots=ld_slots, algo=algo, status=status)
 
 
 @_attention_forward_op.register_fake
 def _attention_forward_fake(hidden_states, attention_mask, qkv_weight, qkv_bias, pos_key, pos_query,
-                            delta_to_local, rel_key, rel_query, num_heads, head_dim, scale, algo):
+                            delta_to_local, rel_key, rel_query, num_heads, head_dim, scale, algo, status):
     return hidden_states.new_empty(hidden_states.shape[0], hidden_states.shape[1], num_heads * head_dim)
 
 
@@ -177,6 +178,9 @@ class DisentangledFlashAttention(nn.Module):
         self.register_buffer("_cached_pos_query", None, persistent=False)
         self.register_buffer("_cached_qkv_weight", None, persistent=False)
         self.register_buffer("_cached_qkv_bias", None, persistent=False)
+        # device int32 that the kernels of this layer write if one of their bounded waits expires; an encoder
+        # shares one word between its layers (set_status_word) and reads it in check_device_status()
+        self.register_buffer("_status_word", None, persistent=False)
         self._position_projection_cache: dict[tuple[int, str], B200PreparedPositionPlan] = {}
         self._algo = _cabi.ALGO_AUTO
         self.register_load_state_dict_post_hook(_invalidate_attention_cache_after_load)
@@ -198,6 +202,21 @@ class DisentangledFlashAttention(nn.Module):
         self.position_plan_cache = cache
         self._position_projection_cache.clear()
         return self
+
+    def set_status_word(self, status: torch.Tensor | None) -> "DisentangledFlashAttention":
+        """Use ``status`` (a zeroed CUDA int32 with one element, e.g. shared by all layers of an encoder)."""
+
+        self._status_word = status
+        return self
+
+    def check_device_status(self) -> None:
+        """Raise ``DflError(DFL_ERR_DEVICE_TIMEOUT)`` if a bounded device-side wait of this layer's kernels expired.
+
+        Synchronises the current stream; call it after a batch, not between layers.
+        """
+
+        if self._status_word is not None:
+            _cabi.check_status(self._status_word)
 
     def clear_inference_cache(self) -> None:
         """Invalidate every tensor derived from this layer's parameters."""
@@ -244,6 +263,7 @@ class DisentangledFlashAttention(nn.Module):
         (projected,) = _cabi.linear_heads(
             relative, projection.weight.contiguous(), projection.bias, n_out=1, heads=self.num_attention_heads,
             head_dim=self.attention_head_size, rows_per_seq=relative.shape[0], algo=self._algo,
+            status=self._status_word,
         )
         return projected[0]
 
@@ -256,6 +276,8 @@ class DisentangledFlashAttention(nn.Module):
         self._validate_device_dtype(self.query_proj.weight)
         self.clear_inference_cache()
         self._prepare_fused_qkv()
+        if self._status_word is None or self._status_word.device != self.query_proj.weight.device:
+            self._status_word = _cabi.new_status_word(self.query_proj.weight.device)
         if not (self.has_c2p or self.has_p2c):
             return self
         if rel_embeddings is None:
@@ -345,7 +367,7 @@ class DisentangledFlashAttention(nn.Module):
         return _cabi.linear_heads(
             hidden_states.contiguous(), self._cached_qkv_weight, self._cached_qkv_bias, n_out=3,
             heads=self.num_attention_heads, head_dim=self.attention_head_size,
-            rows_per_seq=hidden_states.shape[1], algo=self._algo,
+            rows_per_seq=hidden_states.shape[1], algo=self._algo, status=self._status_word,
         )
 
     def forward_prepared(self, hidden_states: torch.Tensor, attention_mask: torch.Tensor,
@@ -387,6 +409,7 @@ class DisentangledFlashAttention(nn.Module):
             self.attention_head_size,
             1.0 / self._scale(scale_factor),
             self._algo,
+            self._status_word,
         )
         return output, None
 

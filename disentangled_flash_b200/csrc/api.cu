@@ -31,6 +31,27 @@ const char* dfl_status_string(int status) {
 
 const char* dfl_last_error(void) { return last_error_buffer(); }
 
+int dfl_check_status(int32_t* status_dev, void* stream) {
+  if (!status_dev) return fail(DFL_ERR_BAD_ARG, "null status word");
+  cudaStream_t s = (cudaStream_t)stream;
+  int32_t code = 0;
+  cudaError_t e = cudaMemcpyAsync(&code, status_dev, sizeof(code), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "reading the status word: %s", cudaGetErrorString(e));
+  if (code == 0) return DFL_OK;
+  e = cudaMemsetAsync(status_dev, 0, sizeof(code), s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "clearing the status word: %s", cudaGetErrorString(e));
+  return fail(DFL_ERR_DEVICE_TIMEOUT, "a bounded device-side wait expired (wait code %d); outputs since the last check are invalid",
+              (int)code);
+}
+
+int dfl_selftest_bounded_wait(int32_t* status_dev, uint32_t limit_us, void* stream) {
+  if (!status_dev) return fail(DFL_ERR_BAD_ARG, "null status word");
+  if (limit_us < 1 || limit_us > 100000) return fail(DFL_ERR_BAD_ARG, "limit_us must be in 1..100000");
+  return launch_selftest_bounded_wait(status_dev, limit_us, (cudaStream_t)stream);
+}
+
 int dfl_build_position_lut(int seq_len, int position_buckets, int max_relative_positions, int span,
                            int uses_position_bias, int32_t* lut_dev, int64_t* active_dev,
                            int32_t* n_active_dev, void* stream) {
@@ -82,6 +103,7 @@ int dfl_qkv_proj(const DflLinearParams* p, void* stream) {
   g.batch = 1; g.stride_x = 0; g.stride_w = 0; g.w_mod = 1; g.stride_c = 0; g.ldc = g.N;
   g.head_split = 1; g.heads = p->heads; g.head_dim = p->head_dim; g.rows_per_seq = p->rows_per_seq;
   g.dtype = p->dtype;
+  g.status = p->status;
   if (use_tensor_cores(p->dtype, p->algo)) return launch_gemm_tc(g, (cudaStream_t)stream);
   return launch_gemm_simt(g, (cudaStream_t)stream);
 }
@@ -116,6 +138,7 @@ int dfl_pos_scores(const DflPosScoreParams* p, void* stream) {
     g.ldc = p->ld_slots;
     g.head_split = 0; g.heads = p->heads; g.head_dim = p->head_dim; g.rows_per_seq = p->seq_len;
     g.dtype = p->dtype;
+    g.status = p->status;
     rc = use_tensor_cores(p->dtype, p->algo) ? launch_gemm_tc(g, (cudaStream_t)stream)
                                              : launch_gemm_simt(g, (cudaStream_t)stream);
   }

@@ -29,7 +29,6 @@
 // still work on the last key tile of the previous item; the second C2P block of an item goes through the P and O
 // columns, which are idle between the read-out of one item and the first PV of the next.
 //   warps 14-15 idle (they complete the fourth warpgroup, whose registers go to the softmax warps)
-#include <mutex>
 #include <type_traits>
 
 #include "attention_tc_common.cuh"
@@ -1131,26 +1130,11 @@ int launch_rel_typed(const DflAttnRelParams& p, cudaStream_t stream) {
   if (rc != DFL_OK) return rc;
 
   auto kernel = attention_rel_kernel<T, D>;
-  // One-time configuration per device and kernel instance (the opt-in to large dynamic shared memory is a
-  // per-device attribute), guarded against concurrent first calls from several host threads.
-  static std::mutex config_mutex;
-  static int sm_counts[kMaxDevices] = {0};
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) return fail(DFL_ERR_LAUNCH, "current device: %s", cudaGetErrorString(e));
+  static KernelDeviceConfig config;   // per instantiation
   int sm_count = 0;
-  {
-    std::lock_guard<std::mutex> lock(config_mutex);
-    if (sm_counts[dev] == 0) {
-      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LO::total);
-      if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "attention_rel smem opt-in: %s", cudaGetErrorString(e));
-      int count = 0;
-      e = cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
-      if (e != cudaSuccess || count < 1) return fail(DFL_ERR_LAUNCH, "SM count: %s", cudaGetErrorString(e));
-      sm_counts[dev] = count;
-    }
-    sm_count = sm_counts[dev];
-  }
+  rc = configure_kernel(config, kernel, LO::total, &sm_count, "attention_rel_kernel");
+  if (rc != DFL_OK) return rc;
+  cudaError_t e;
   int* status_word = p.status;
   if (!status_word) {
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status_word), g_attn_rel_status);

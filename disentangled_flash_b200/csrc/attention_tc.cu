@@ -61,7 +61,7 @@ struct Layout {
   static constexpr int kKV = 2 * kSub * kKSub;                  // K then V
   static constexpr int kBias = BM * C_PITCH + BN * P_PITCH;    // one relative-score stage
   static constexpr int kTmemCols = (COL_O + D) <= 256 ? 256 : 512;
-  static constexpr int kBiasStages = D == 128 ? 1 : 1;
+  static constexpr int kBiasStages = 1;                         // relative-score stages (shared memory leaves room for one)
   static constexpr int offQ = 0;
   static constexpr int offKV = offQ + kQ;
   static constexpr int offBias = offKV + KV_STAGES * kKV;
@@ -382,12 +382,9 @@ int launch_typed(const DflAttnParams& p, cudaStream_t stream) {
   if (smem > kMaxSmem) return fail(DFL_ERR_TOO_LARGE, "seq_len %d needs %d bytes of shared memory", L, smem);
 
   auto kernel = attention_tc_kernel<T, D>;
-  static int configured_smem = 0;  // per instantiation
-  if (smem > configured_smem) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "attention_tc smem opt-in: %s", cudaGetErrorString(e));
-    configured_smem = smem;
-  }
+  static KernelDeviceConfig config;   // per instantiation
+  rc = configure_kernel(config, kernel, smem, nullptr, "attention_tc_kernel");
+  if (rc != DFL_OK) return rc;
   int* status_word = p.status;
   if (!status_word) {
     cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status_word), g_attn_status);

@@ -8,6 +8,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <mutex>
 
 #include "../../include/dfl_b200.h"
 
@@ -36,6 +37,37 @@ inline int check_launch(const char* what) {
 
 // Launchers keep their one-time configuration (shared-memory opt-in, SM count, symbol addresses) per device.
 constexpr int kMaxDevices = 64;
+
+// One-time launch configuration of one kernel instance, kept per device: the opt-in to large dynamic shared
+// memory is a per-device attribute of the kernel, and the grid of a persistent kernel follows the device's SM
+// count.  One object per kernel instance (a function-local static of its launcher); first calls from several
+// host threads are serialised.
+struct KernelDeviceConfig {
+  std::mutex mutex;
+  int smem_opted_in[kMaxDevices] = {0};
+  int sm_count[kMaxDevices] = {0};
+};
+template <typename Kernel>
+inline int configure_kernel(KernelDeviceConfig& cfg, Kernel kernel, int smem_bytes, int* sm_count, const char* what) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return fail(DFL_ERR_LAUNCH, "%s: current device: %s", what, cudaGetErrorString(e));
+  std::lock_guard<std::mutex> lock(cfg.mutex);
+  if (smem_bytes > cfg.smem_opted_in[dev]) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "%s: shared-memory opt-in: %s", what, cudaGetErrorString(e));
+    cfg.smem_opted_in[dev] = smem_bytes;
+  }
+  if (cfg.sm_count[dev] == 0) {
+    int count = 0;
+    e = cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess || count < 1) return fail(DFL_ERR_LAUNCH, "%s: SM count: %s", what, cudaGetErrorString(e));
+    cfg.sm_count[dev] = count;
+  }
+  if (sm_count) *sm_count = cfg.sm_count[dev];
+  return DFL_OK;
+}
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -95,6 +127,7 @@ struct GemmDesc {
   int head_split;       // 1: head-split epilogue, 0: row-major
   int heads, head_dim, rows_per_seq;
   int dtype;
+  int* status;          // device status word of the call, or null (the tcgen05 GEMM then uses the library's word)
 };
 int launch_gemm_simt(const GemmDesc& g, cudaStream_t stream);
 int launch_gemm_tc(const GemmDesc& g, cudaStream_t stream);
@@ -103,6 +136,7 @@ int launch_attention_simt(const DflAttnParams& p, cudaStream_t stream);
 int launch_attention_tc(const DflAttnParams& p, cudaStream_t stream);
 bool attention_rel_supported(const DflAttnRelParams& p);
 int launch_attention_rel(const DflAttnRelParams& p, cudaStream_t stream);
+int launch_selftest_bounded_wait(int* status, uint32_t limit_us, cudaStream_t stream);
 int launch_expand_rel_tables(const void* pos, const int32_t* lut, void* rel, int heads, int n_active, int seq_len,
                              int head_dim, int dtype, cudaStream_t stream);
 

@@ -148,7 +148,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
-          ok = ptx::mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, &g_gemm_status, 1);
+          ok = ptx::mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, g.status, 1);
           if (!ok) break;
           ptx::mbar_arrive_expect_tx(&full_bar[s], (uint32_t)S::kStage);
           unsigned char* a = smem + s * S::kStage;
@@ -169,14 +169,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
       int lt = 0;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
         const int acc = lt & 1;
-        ok = ptx::mbar_wait(&tmem_empty_bar[acc], ((uint32_t)(lt >> 1) & 1u) ^ 1u, abort_flag, &g_gemm_status, 4);
+        ok = ptx::mbar_wait(&tmem_empty_bar[acc], ((uint32_t)(lt >> 1) & 1u) ^ 1u, abort_flag, g.status, 4);
         if (!ok) break;
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * TN;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
-          ok = ptx::mbar_wait(&full_bar[s], ph, abort_flag, &g_gemm_status, 2);
+          ok = ptx::mbar_wait(&full_bar[s], ph, abort_flag, g.status, 2);
           if (!ok) break;
           ptx::tc_fence_after();
           // descriptors differ from the stage-0 ones only in the 16-byte-granular address field
@@ -202,7 +202,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
       int m0, n0, z;
       tile_coords(tile, m0, n0, z);
       const int acc = lt & 1;
-      if (ready) ready = ptx::mbar_wait(&tmem_full_bar[acc], (uint32_t)(lt >> 1) & 1u, abort_flag, &g_gemm_status, 3);
+      if (ready) ready = ptx::mbar_wait(&tmem_full_bar[acc], (uint32_t)(lt >> 1) & 1u, abort_flag, g.status, 3);
       ptx::tc_fence_after();
       const int row = warp * 32 + lane;
       const int m = m0 + row;
@@ -271,16 +271,14 @@ int launch_bk(const GemmDesc& g, cudaStream_t stream) {
   if (rc != DFL_OK) return rc;
 
   auto kernel = gemm_tc_kernel<T, BK>;
-  static bool configured = false;  // per template instantiation
-  static int num_sms = 0;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
-    if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "gemm_tc smem opt-in: %s", cudaGetErrorString(e));
-    int dev = 0;
-    cudaGetDevice(&dev);
-    e = cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess || num_sms < 1) return fail(DFL_ERR_LAUNCH, "SM count query failed");
-    configured = true;
+  static KernelDeviceConfig config;   // per template instantiation
+  int num_sms = 0;
+  rc = configure_kernel(config, kernel, S::kTotal, &num_sms, "gemm_tc_kernel");
+  if (rc != DFL_OK) return rc;
+  GemmDesc gd = g;
+  if (!gd.status) {
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&gd.status), g_gemm_status);
+    if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "status word: %s", cudaGetErrorString(e));
   }
   const int ncols = g.head_split ? g.N : g.ldc;
   const int tiles_n = (ncols + TN - 1) / TN, tiles_m = (g.M + TM - 1) / TM;
@@ -288,7 +286,7 @@ int launch_bk(const GemmDesc& g, cudaStream_t stream) {
   if (num_tiles > 0x7fffffff) return fail(DFL_ERR_TOO_LARGE, "gemm_tc: too many tiles");
   const int grid = (int)(num_tiles < num_sms ? num_tiles : num_sms);
   const int num_kb = (g.K + BK - 1) / BK;
-  kernel<<<grid, kThreads, S::kTotal, stream>>>(tmap_x, tmap_w, g, num_kb, tiles_n, tiles_m, (int)num_tiles);
+  kernel<<<grid, kThreads, S::kTotal, stream>>>(tmap_x, tmap_w, gd, num_kb, tiles_n, tiles_m, (int)num_tiles);
   return check_launch("gemm_tc_kernel");
 }
 

@@ -51,6 +51,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same with a suspend-time hint: the hardware may park the thread for up to `hint_ns` (it resumes at once
+// when the phase completes), so a waiting warp takes few issue slots from the warps that share its scheduler.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 
 // Bounded wait.  abort_flag lives in shared memory; gstatus may be null.  The polling loop with its
 // time limit is kept out of line: waits are inlined in many places and the kernels are sensitive to
@@ -81,7 +94,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 // Fully inlined bounded wait, for kernels that change their register budget with setmaxnreg (such kernels
 // cannot contain calls to separately compiled device functions).  It is inlined at every wait of those kernels, and
 // they are sensitive to instruction-cache footprint, so it is kept small: the clock (low 32 bits of the nanosecond
-// timer, enough for a limit of two seconds) and the CTA's abort flag are looked at once per 1024 failed polls, and
+// timer, enough for a limit of two seconds) and the CTA's abort flag are looked at once per 64 failed polls (each of
+// which may park the thread for a couple of microseconds), and
 // the code of the wait that gave up is left in a register of the caller instead of being written from here.
 __device__ __forceinline__ uint32_t globaltimer_lo() {
   uint32_t t;
@@ -89,13 +103,14 @@ __device__ __forceinline__ uint32_t globaltimer_lo() {
   return t;
 }
 __device__ __forceinline__ bool mbar_wait_inline(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int& fail_code,
-                                                 int code) {
+                                                 int code, uint32_t limit_ns = (uint32_t)kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint32_t t0 = globaltimer_lo();
   uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 1023u) != 0) continue;
-    if (*abort_flag || globaltimer_lo() - t0 > (uint32_t)kWaitLimitNs) {
+  while (!mbar_try_wait_hint(bar, parity, 2000u)) {
+    if ((++spins & 63u) != 0) continue;
+    if (*abort_flag) return false;   // another wait of the CTA gave up
+    if (globaltimer_lo() - t0 > limit_ns) {
       *abort_flag = 1;     // every other wait of the CTA gives up at its next look
       fail_code = code;    // reported by the caller once, when it leaves its role
       return false;

@@ -56,6 +56,23 @@ DFL_API const char* dfl_status_string(int status);
 DFL_API const char* dfl_last_error(void);
 
 /*
+ * Device status word.  The tcgen05 kernels wait on hardware barriers with a time limit (two seconds); a wait
+ * that runs out makes its CTA skip the rest of its work, free its tensor memory and return, after writing a
+ * non-zero code (which wait gave up) to the `status` word of the call - a device int32 owned by the caller and
+ * zeroed by it before first use; calls given no status word use a word inside the library.  Nothing on the hot
+ * path reads the word.  dfl_check_status() is the read-out: it waits for `stream`, copies the word to the host,
+ * and if it is non-zero clears it and returns DFL_ERR_DEVICE_TIMEOUT (dfl_last_error() names the code; the
+ * outputs of the calls since the previous check are then not valid).  The reference has no counterpart: its
+ * Triton kernel has no device-side waits.
+ *
+ * dfl_selftest_bounded_wait() is a diagnostic for that path: one CTA allocates tensor memory, waits on a
+ * barrier nobody arrives at with a limit of `limit_us` microseconds (1..100000), gives up, frees its tensor
+ * memory and records code 99 in `status_dev`.  It never traps and never waits without a limit.
+ */
+DFL_API int dfl_check_status(int32_t* status_dev, void* stream);
+DFL_API int dfl_selftest_bounded_wait(int32_t* status_dev, uint32_t limit_us, void* stream);
+
+/*
  * Log-bucket relative-position index builder (bit-exact).
  * Replaces SharedPositionPlanCache.compact (position.py:89-128) and
  * make_log_bucket_position (_reference.py:115-136), which the reference
@@ -93,6 +110,7 @@ typedef struct DflLinearParams {
   int32_t rows_per_seq; /* L; M must be a multiple of it                       */
   int32_t dtype;        /* DFL_F16 / DFL_BF16 / DFL_F32                        */
   int32_t algo;         /* DFL_ALGO_*                                          */
+  int32_t* status;      /* optional device int32, see dfl_check_status()       */
 } DflLinearParams;
 DFL_API int dfl_qkv_proj(const DflLinearParams* p, void* stream);
 
@@ -125,6 +143,7 @@ typedef struct DflPosScoreParams {
   int32_t batch, heads, seq_len, head_dim;
   int32_t n_active, ld_slots;
   int32_t dtype, algo;
+  int32_t* status;        /* optional device int32, see dfl_check_status() */
 } DflPosScoreParams;
 DFL_API int dfl_pos_scores(const DflPosScoreParams* p, void* stream);
 
@@ -143,7 +162,10 @@ typedef struct DflAttnParams {
   const void* v;          /* [B,H,L,d] */
   const void* c2p;        /* [B,H,L,ld_slots] or NULL (term disabled) */
   const void* p2c;        /* [B,H,L,ld_slots] or NULL (term disabled) */
-  const int32_t* lut;     /* [2L-1]; may be NULL when both terms are disabled */
+  const int32_t* lut;     /* [2L-1]; may be NULL when both terms are disabled.  Must come from
+                             dfl_build_position_lut or have its shape: non-decreasing in the delta index with
+                             steps of 0 or 1 and entries in [0, ld_slots) - the tcgen05 kernel stages one
+                             contiguous window of slots per tile and clamps anything outside it */
   const void* mask;       /* [B,L], mask_elem_size bytes per element, non-zero = keep */
   void*       out;        /* [B,L,H*d] */
   int32_t*    status;     /* optional device int32: set non-zero if a bounded wait expired */

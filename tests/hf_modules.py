@@ -1,4 +1,4 @@
-"""Minimal DeBERTa-v2/v3 encoder stack with Hugging Face module names.
+"""Minimal DeBERTa-v2/v3 encoder stack with Hugging Face module names (test and benchmark harness).
 
 The fused kernels replace only ``layer.attention.self``; everything else in a
 layer stays ordinary PyTorch.  Real deployments pass a Transformers
@@ -18,7 +18,7 @@ import torch
 from torch import nn
 from torch.nn import functional as F
 
-from .config import normalise_pos_att_type
+from disentangled_flash_b200.config import normalise_pos_att_type
 
 _ACTIVATIONS = {"gelu": F.gelu, "relu": F.relu, "silu": F.silu, "swish": F.silu, "tanh": torch.tanh,
                 "gelu_new": lambda x: F.gelu(x, approximate="tanh")}

@@ -311,7 +311,7 @@ def test_encoder_wrapper_matches_oracle_encoder(dtype_name):
     import copy
 
     import disentangled_flash_b200 as df
-    from disentangled_flash_b200 import hf_modules
+    import hf_modules
 
     dtype = DTYPES[dtype_name]
     # the PyTorch layers around the attention must not silently use TF32 (cuDNN convolutions do by default)

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import disentangled_flash_b200 as df
-from disentangled_flash_b200 import hf_modules
+import hf_modules
 
 
 def small_config(**kw):
