@@ -441,9 +441,6 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           const int rr = e / kVec, v = e - rr * kVec;
           *reinterpret_cast<uint4*>(out + (long long)rr * H * D + v * 8) = mine;
         }
-        // keeps the phase of o_free equal to the item count; also orders the next use of the scratch
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&bars->o_free);
       } else {
         const int i = i0 + r;
         const bool row_ok = i < L;
@@ -949,6 +946,7 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         uint32_t c_q = 0, c_k = 0, c_v = 0, c_rk = 0;   // loads consumed (stage / phase as in the loader)
         uint32_t c_s = 0, c_xc = 0, c_xp = 0, c_p = 0;  // S tiles, C2P blocks through XC, P2C halves, PVs issued
         uint32_t rq_alloc = 0;                          // rel_query blocks handed to items so far
+        uint32_t c_items = 0;                           // items with kept rows started so far
         bool ok = true;
 
         // D[128 x 128] = A[128 x d] * B[128 x d]^T, both operands K-major tiles in shared memory
@@ -1037,8 +1035,12 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
         for (; it < n_items && ok; it += gridDim.x, ++k) {
           const bool has_next = n_items - it > (int)gridDim.x;
-          // the output accumulator of the previous item has been read out (every item completes a phase of o_free)
-          if (k > 0) ok = wait1(&bars->o_free, (uint32_t)(k - 1) & 1u, 38);
+          // The output accumulator of the previous item with kept rows has been read out (o_free completes one phase per
+          // such item; this thread is never more than one phase behind, so parities cannot alias).
+          if (cur.any_kept) {
+            if (c_items > 0) ok = wait1(&bars->o_free, (c_items - 1u) & 1u, 38);
+            ++c_items;
+          }
           if (!ok) break;
           if (cur.any_kept) {
             const int n = cur.n;
