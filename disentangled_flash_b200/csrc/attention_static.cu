@@ -14,13 +14,13 @@ namespace dfl {
 namespace {
 
 constexpr size_t kStaticScratchBytes = DFL_STATIC_SCRATCH_BYTES;
-constexpr int kMaxDevices = 64;
 
 // Lives in every CUDA context that loads the library, until the context is destroyed.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 // In host code the array's name is only a handle: the device address has to be asked for, once per
-// device, while that device is current.
+// device, while that device is current.  The address is cached for the life of the process: it stays valid
+// until the device's context is destroyed (after cudaDeviceReset the library must be reloaded).
 std::mutex g_setup_mutex;
 unsigned char* g_scratch_addr[kMaxDevices] = {nullptr};
 
@@ -52,18 +52,28 @@ size_t dfl_static_scratch_bytes(void) { return kStaticScratchBytes; }
 
 int dfl_attention_fwd_static(const DflAttnTablesParams* p, void* stream) {
   if (!p) return fail(DFL_ERR_BAD_ARG, "null params");
+  // Everything that bounds the scratch size is checked before the size is computed, so that the product below
+  // cannot wrap: batch*heads <= 2^16, seq_len <= 2^14, slots <= 2^15, 4 bytes -> below 2^47.
+  if (p->dtype != DFL_F16 && p->dtype != DFL_BF16 && p->dtype != DFL_F32) return fail(DFL_ERR_BAD_ARG, "unknown dtype %d", p->dtype);
+  if (p->head_dim != 32 && p->head_dim != 64 && p->head_dim != 128)
+    return fail(DFL_ERR_UNSUPPORTED, "head_dim %d not in {32,64,128}", p->head_dim);
   if (p->batch < 1 || p->heads < 1 || p->seq_len < 1) return fail(DFL_ERR_BAD_ARG, "non-positive size");
+  if (p->seq_len > 16384) return fail(DFL_ERR_TOO_LARGE, "seq_len %d > 16384", p->seq_len);
+  if ((long long)p->batch * p->heads > 65535) return fail(DFL_ERR_TOO_LARGE, "batch*heads > 65535");
   const bool has_c2p = p->pos_key != nullptr, has_p2c = p->pos_query != nullptr;
   if ((has_c2p || has_p2c) && p->n_active < 1) return fail(DFL_ERR_BAD_ARG, "n_active must be positive");
+  if ((has_c2p || has_p2c) && p->n_active > 2 * p->seq_len)
+    return fail(DFL_ERR_BAD_ARG, "n_active %d exceeds the 2*seq_len relative distances", p->n_active);
 
-  const size_t es = p->dtype == DFL_F32 ? 4 : 2;
+  const unsigned long long es = p->dtype == DFL_F32 ? 4 : 2;
   const int ld = has_c2p || has_p2c ? (p->n_active + 7) / 8 * 8 : 0;
-  size_t one = (size_t)p->batch * p->heads * p->seq_len * ld * es;
+  unsigned long long one = (unsigned long long)p->batch * (unsigned long long)p->heads * (unsigned long long)p->seq_len *
+                           (unsigned long long)ld * es;
   one = (one + 255) / 256 * 256;
-  const size_t need = one * ((has_c2p ? 1 : 0) + (has_p2c ? 1 : 0));
+  const unsigned long long need = one * ((has_c2p ? 1 : 0) + (has_p2c ? 1 : 0));
   if (need > kStaticScratchBytes)
     return fail(DFL_ERR_TOO_LARGE,
-                "relative-score scratch of %zu bytes exceeds the built-in %zu bytes; "
+                "relative-score scratch of %llu bytes exceeds the built-in %zu bytes; "
                 "use dfl_pos_scores + dfl_attention_fwd with caller-provided buffers",
                 need, kStaticScratchBytes);
 

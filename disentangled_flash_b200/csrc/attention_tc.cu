@@ -140,19 +140,26 @@ __device__ __forceinline__ void softmax_role(const RoleCtx& c, const DflAttnPara
       const unsigned char* c_row = stage + r * C_PITCH - c_lo;
       const uint32_t p_lo = c.lut_s[LUT_LO_PAD + c.i0 - j0 + (L - 1) - (BN - 1)] & ~15u;
       const unsigned char* p_row = stage + BM * C_PITCH - p_lo;
-      auto elem = [](const unsigned char* base, uint32_t off) { return *reinterpret_cast<const uint16_t*>(base + off); };
+      // A slot table of the builder's shape (non-decreasing, steps of 0 or 1) keeps every offset inside the staged
+      // window; for any other table the offset is clamped into the window, so that a wrong table gives wrong
+      // scores but never a read outside the row's stage.
+      auto elem = [](const unsigned char* base, uint32_t lo, uint32_t off, uint32_t pitch) {
+        const uint32_t rel = min(off - lo, pitch - 2u);   // off < lo wraps to a huge value and is clamped as well
+        return *reinterpret_cast<const uint16_t*>(base + lo + rel);
+      };
       if (c.has_c2p && c.has_p2c) {
 #pragma unroll
         for (int jj = 0; jj < BN; ++jj) {
           const uint32_t off = lut_i[-jj];
-          s[jj] = Pack2<T>::add(Pack2<T>::add(s[jj], elem(c_row, off)), elem(p_row + jj * P_PITCH, off));
+          s[jj] = Pack2<T>::add(Pack2<T>::add(s[jj], elem(c_row, c_lo, off, C_PITCH)),
+                                elem(p_row + jj * P_PITCH, p_lo, off, P_PITCH));
         }
       } else if (c.has_c2p) {
 #pragma unroll
-        for (int jj = 0; jj < BN; ++jj) s[jj] = Pack2<T>::add(s[jj], elem(c_row, lut_i[-jj]));
+        for (int jj = 0; jj < BN; ++jj) s[jj] = Pack2<T>::add(s[jj], elem(c_row, c_lo, lut_i[-jj], C_PITCH));
       } else {
 #pragma unroll
-        for (int jj = 0; jj < BN; ++jj) s[jj] = Pack2<T>::add(s[jj], elem(p_row + jj * P_PITCH, lut_i[-jj]));
+        for (int jj = 0; jj < BN; ++jj) s[jj] = Pack2<T>::add(s[jj], elem(p_row + jj * P_PITCH, p_lo, lut_i[-jj], P_PITCH));
       }
       ptx::mbar_arrive(&bars->bias_empty[bs]);
     }
@@ -220,7 +227,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     for (int e = threadIdx.x; e < n_lut; e += kThreads) {
       int src = e - LUT_LO_PAD;
       src = src < 0 ? 0 : (src > 2 * L - 2 ? 2 * L - 2 : src);
-      lut_s[e] = (uint16_t)(2 * p.lut[src]);
+      // entries outside [0, ld_slots) (a table that did not come from dfl_build_position_lut) are clamped
+      int slot = p.lut[src];
+      slot = slot < 0 ? 0 : (slot >= p.ld_slots ? p.ld_slots - 1 : slot);
+      lut_s[e] = (uint16_t)(2 * slot);
     }
   }
   // key keep-mask as bits: word w covers keys [32w, 32w+32); keys >= L are 0

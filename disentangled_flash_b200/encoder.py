@@ -1,25 +1,26 @@
 """Encoder-level drop-in: ``optimize_deberta`` / ``enable_deberta_inference``.
 
-Mirror of the reference's encoder wrapper and public API
-(``src/disentangled_flash/deberta.py:38-447``).  The wrapper keeps the
-Hugging Face layer list, ``rel_embeddings``, ``LayerNorm`` and ``conv`` by
-reference (checkpoint keys do not change), swaps every
-``layer.attention.self`` for :class:`DisentangledFlashAttention`, prepares one
-tuple of per-layer plans per sequence-length bucket, and runs the layer loop
-with the 2-D padding mask and the prepared plans: no ``[B,1,L,L]`` mask and no
-``[L,L]`` relative-position tensor is ever built.
+Plays the role of the reference's encoder wrapper and public API
+(``src/disentangled_flash/deberta.py:38-447``): the names, signatures,
+exception classes and messages a user of the reference relies on are kept, the
+implementation is this package's own.
 
-Everything outside ``attention.self`` (attention output projection, FFN,
-layer norms, the layer-0 convolution) stays the caller's PyTorch modules.
-There is a single backend; ``backend="triton"`` is accepted as the legacy name
-of the fused backend, ``backend="torch"`` is refused because no CPU/PyTorch
-attention ships with this package.
+The wrapper adopts a Hugging Face ``DebertaV2Encoder`` without changing a
+checkpoint key: the layer list, ``rel_embeddings``, ``LayerNorm`` and ``conv``
+are the caller's modules, only ``layer.attention.self`` is exchanged for
+:class:`DisentangledFlashAttention`.  Per sequence-length bucket it keeps one
+tuple of per-layer position plans (a ``_BucketTable``); a forward pass walks the
+layers with the 2-D padding mask and the active tuple.  No ``[B,1,L,L]`` mask
+and no ``[L,L]`` relative-position tensor exists at any point.
+
+Everything outside ``attention.self`` (attention output projection, FFN, layer
+norms, the layer-0 convolution) stays ordinary PyTorch.  There is one backend;
+``backend="triton"`` is accepted as the legacy name of the fused backend and
+``backend="torch"`` is refused because no CPU/PyTorch attention ships here.
 """
 
 from __future__ import annotations
 
-import inspect
-import types
 from collections.abc import Callable, Iterable, Mapping
 from dataclasses import dataclass
 from typing import Any
@@ -27,11 +28,15 @@ from typing import Any
 import torch
 from torch import nn
 
+from . import _cabi
 from .attention import B200PreparedPositionPlan, DisentangledFlashAttention
 from .config import normalise_pos_att_type
 from .position import SharedPositionPlanCache
 
 FUSED_BACKENDS = ("b200", "triton")
+_REFUSED_BACKENDS = ("torch", "optimized")
+
+Plans = tuple[B200PreparedPositionPlan, ...]
 
 
 @dataclass
@@ -43,11 +48,65 @@ class BaseModelOutput:
     attentions: tuple[torch.Tensor, ...] | None = None
 
     def __getitem__(self, index: int) -> Any:
-        present = tuple(v for v in (self.last_hidden_state, self.hidden_states, self.attentions) if v is not None)
-        return present[index]
+        fields = (self.last_hidden_state, self.hidden_states, self.attentions)
+        return [field for field in fields if field is not None][index]
 
 
-def _invalidate_encoder_cache_after_load(module: nn.Module, _incompatible_keys: Any) -> None:
+class _BucketTable:
+    """Prepared plans per sequence length, and which of them is active."""
+
+    def __init__(self) -> None:
+        self.by_length: dict[int, Plans] = {}
+        self.active_length: int | None = None
+        self.active: Plans | None = None
+
+    def reset(self) -> None:
+        self.by_length.clear()
+        self.active_length = None
+        self.active = None
+
+    def select(self, sequence_length: int) -> None:
+        plans = self.by_length.get(sequence_length)
+        if plans is None:
+            raise ValueError(
+                f"sequence length {sequence_length} was not prepared; available buckets: {sorted(self.by_length)}"
+            )
+        self.active_length, self.active = sequence_length, plans
+
+    def require(self, lengths: Iterable[int]) -> tuple[int, ...]:
+        wanted = _unique_lengths(lengths)
+        absent = [length for length in wanted if length not in self.by_length]
+        if absent:
+            raise ValueError(f"unprepared bucket lengths: {absent}")
+        return wanted
+
+
+def _unique_lengths(lengths: int | Iterable[int]) -> tuple[int, ...]:
+    items = [lengths] if isinstance(lengths, int) else list(lengths)
+    seen: list[int] = []
+    for item in items:
+        value = int(item)
+        if value not in seen:
+            seen.append(value)
+    return tuple(seen)
+
+
+def _adopt_attention(layer: nn.Module, config: Any, cache: SharedPositionPlanCache, fp32_precision: str) -> None:
+    """Exchange ``layer.attention.self`` for the fused module, carrying parameters, placement and mode over."""
+
+    current = layer.attention.self
+    if isinstance(current, DisentangledFlashAttention):
+        current.set_position_plan_cache(cache)
+        return
+    fused = DisentangledFlashAttention(config, position_plan_cache=cache, fp32_precision=fp32_precision)
+    fused.load_state_dict(current.state_dict(), strict=True)
+    anchor = current.query_proj.weight
+    fused.to(device=anchor.device, dtype=anchor.dtype)
+    fused.train(current.training)
+    layer.attention.self = fused
+
+
+def _drop_plans_after_load(module: nn.Module, _incompatible_keys: Any) -> None:
     module.clear_inference_cache()
 
 
@@ -62,7 +121,7 @@ class DebertaV2InferenceEncoder(nn.Module):
     def __init__(self, source_encoder: nn.Module, config: Any, *, backend: str = "b200",
                  fp32_precision: str = "strict") -> None:
         super().__init__()
-        if backend in ("torch", "optimized"):
+        if backend in _REFUSED_BACKENDS:
             raise ValueError(
                 f"backend={backend!r} is not available: this package ships only the fused CUDA backend "
                 f"(use one of {FUSED_BACKENDS})"
@@ -71,58 +130,44 @@ class DebertaV2InferenceEncoder(nn.Module):
             raise ValueError(f"backend must be one of {FUSED_BACKENDS}")
         if not hasattr(source_encoder, "layer"):
             raise TypeError("source_encoder does not look like a DebertaV2Encoder")
-
         self.backend = backend
         self.fp32_precision = fp32_precision
-        self.relative_attention = getattr(source_encoder, "relative_attention", False)
-        self.max_relative_positions = getattr(
-            source_encoder, "max_relative_positions", getattr(config, "max_position_embeddings", 512)
-        )
-        self.position_buckets = getattr(source_encoder, "position_buckets", -1)
-        self.norm_rel_ebd = list(getattr(source_encoder, "norm_rel_ebd", ["none"]))
         self.gradient_checkpointing = False
 
-        # Same attribute names as Hugging Face: checkpoint keys stay stable.
+        # geometry of the relative-position scheme, as the source encoder states it
+        self.relative_attention = bool(getattr(source_encoder, "relative_attention", False))
+        fallback_positions = getattr(config, "max_position_embeddings", 512)
+        self.max_relative_positions = getattr(source_encoder, "max_relative_positions", fallback_positions)
+        self.position_buckets = getattr(source_encoder, "position_buckets", -1)
+        self.norm_rel_ebd = list(getattr(source_encoder, "norm_rel_ebd", ["none"]))
+
+        # the caller's modules under their Hugging Face names: checkpoint keys do not move
         self.layer = source_encoder.layer
-        if self.relative_attention:
-            self.rel_embeddings = source_encoder.rel_embeddings
-        if hasattr(source_encoder, "LayerNorm"):
-            self.LayerNorm = source_encoder.LayerNorm
+        for name in ("rel_embeddings", "LayerNorm"):
+            if (name != "rel_embeddings" or self.relative_attention) and hasattr(source_encoder, name):
+                setattr(self, name, getattr(source_encoder, name))
         self.conv = getattr(source_encoder, "conv", None)
 
-        span = self.position_buckets if self.position_buckets > 0 else self.max_relative_positions
-        types_ = normalise_pos_att_type(getattr(config, "pos_att_type", ()) or ())
+        terms = set(normalise_pos_att_type(getattr(config, "pos_att_type", ()) or ()))
         self.position_plan_cache = SharedPositionPlanCache(
             position_buckets=self.position_buckets,
             max_relative_positions=self.max_relative_positions,
-            position_embedding_size=span,
-            uses_position_bias=self.relative_attention and bool({"c2p", "p2c"} & set(types_)),
+            position_embedding_size=self.position_buckets if self.position_buckets > 0 else self.max_relative_positions,
+            uses_position_bias=self.relative_attention and not terms.isdisjoint(("c2p", "p2c")),
         )
-
         for layer in self.layer:
-            original = layer.attention.self
-            if isinstance(original, DisentangledFlashAttention):
-                replacement = original.set_position_plan_cache(self.position_plan_cache)
-            else:
-                replacement = DisentangledFlashAttention(
-                    config, position_plan_cache=self.position_plan_cache, fp32_precision=fp32_precision
-                )
-                replacement.load_state_dict(original.state_dict(), strict=True)
-                replacement.to(device=original.query_proj.weight.device, dtype=original.query_proj.weight.dtype)
-                replacement.train(original.training)
-            layer.attention.self = replacement
+            _adopt_attention(layer, config, self.position_plan_cache, fp32_precision)
 
-        self._prepared_plans: dict[int, tuple[B200PreparedPositionPlan, ...]] = {}
-        self._active_sequence_length: int | None = None
-        self._active_plans: tuple[B200PreparedPositionPlan, ...] | None = None
-        self.register_load_state_dict_post_hook(_invalidate_encoder_cache_after_load)
+        self._buckets = _BucketTable()
+        self._status_word: torch.Tensor | None = None
+        self.register_load_state_dict_post_hook(_drop_plans_after_load)
 
     # ----------------------------------------------------------- HF-like API
     def get_rel_embedding(self) -> torch.Tensor | None:
-        relative = self.rel_embeddings.weight if self.relative_attention else None
-        if relative is not None and "layer_norm" in self.norm_rel_ebd:
-            relative = self.LayerNorm(relative)
-        return relative
+        if not self.relative_attention:
+            return None
+        table = self.rel_embeddings.weight
+        return self.LayerNorm(table) if "layer_norm" in self.norm_rel_ebd else table
 
     def get_attention_mask(self, attention_mask: torch.Tensor) -> torch.Tensor:
         if attention_mask.dim() != 2:
@@ -132,28 +177,42 @@ class DebertaV2InferenceEncoder(nn.Module):
     def get_rel_pos(self, *args: Any, **kwargs: Any) -> None:
         return None
 
-    def _attention_modules(self) -> tuple[DisentangledFlashAttention, ...]:
-        return tuple(layer.attention.self for layer in self.layer)
+    def _attention_modules(self) -> list[DisentangledFlashAttention]:
+        return [layer.attention.self for layer in self.layer]
+
+    # the reference's tests and tooling look these up
+    @property
+    def _prepared_plans(self) -> dict[int, Plans]:
+        return self._buckets.by_length
+
+    @property
+    def _active_sequence_length(self) -> int | None:
+        return self._buckets.active_length
+
+    @property
+    def _active_plans(self) -> Plans | None:
+        return self._buckets.active
 
     # ---------------------------------------------------- cache invalidation
     def clear_inference_cache(self) -> None:
-        self._prepared_plans.clear()
-        self._active_sequence_length = None
-        self._active_plans = None
+        """Forget every bucket and everything derived from the parameters (three triggers: ``train()``,
+        ``_apply`` i.e. ``.to()/.half()/...``, and ``load_state_dict``)."""
+
+        self._buckets.reset()
         self.position_plan_cache.clear()
         for attention in self._attention_modules():
             attention.clear_inference_cache()
 
     def train(self, mode: bool = True) -> "DebertaV2InferenceEncoder":
-        if mode and hasattr(self, "_prepared_plans"):
+        if mode and "_buckets" in self.__dict__:
             self.clear_inference_cache()
         return super().train(mode)
 
     def _apply(self, fn: Any, recurse: bool = True) -> "DebertaV2InferenceEncoder":
-        result = super()._apply(fn, recurse=recurse)
-        if hasattr(self, "_prepared_plans"):
+        applied = super()._apply(fn, recurse=recurse)
+        if "_buckets" in self.__dict__:
             self.clear_inference_cache()
-        return result
+        return applied
 
     # ------------------------------------------------------------ preparation
     @torch.no_grad()
@@ -162,91 +221,86 @@ class DebertaV2InferenceEncoder(nn.Module):
 
         if self.training:
             raise RuntimeError("prepare_for_inference() requires encoder.eval()")
-        if isinstance(sequence_lengths, int):
-            lengths: tuple[int, ...] = (sequence_lengths,)
-        else:
-            lengths = tuple(dict.fromkeys(int(length) for length in sequence_lengths))
-        if not lengths or any(length < 1 for length in lengths):
+        lengths = _unique_lengths(sequence_lengths)
+        if not lengths or min(lengths) < 1:
             raise ValueError("sequence_lengths must contain positive integers")
-
         self.clear_inference_cache()
-        rel_embeddings = self.get_rel_embedding()
-        attentions = self._attention_modules()
-        for attention in attentions:
-            attention.eval().prepare_for_inference(rel_embeddings)
-        device = attentions[0].query_proj.weight.device
+        relative = self.get_rel_embedding()
+        modules = self._attention_modules()
+        device = modules[0].query_proj.weight.device
+        # one status word for all layers: a bounded device-side wait that expires anywhere in the encoder shows up in
+        # check_device_status()
+        self._status_word = _cabi.new_status_word(device) if device.type == "cuda" else None
+        for module in modules:
+            module.eval()
+            module.prepare_for_inference(relative)
+            module.set_status_word(self._status_word)
         for length in lengths:
-            self._prepared_plans[length] = tuple(a.prepare_shape(length, device) for a in attentions)
-        self.activate_shape(lengths[0])
+            self._buckets.by_length[length] = tuple(module.prepare_shape(length, device) for module in modules)
+        self._buckets.select(lengths[0])
         return self
 
     def activate_shape(self, sequence_length: int) -> "DebertaV2InferenceEncoder":
         """Select a prebuilt bucket outside the hot path."""
 
-        try:
-            plans = self._prepared_plans[sequence_length]
-        except KeyError as error:
-            raise ValueError(
-                f"sequence length {sequence_length} was not prepared; available buckets: "
-                f"{sorted(self._prepared_plans)}"
-            ) from error
-        self._active_sequence_length = sequence_length
-        self._active_plans = plans
+        self._buckets.select(sequence_length)
         return self
 
+    def check_device_status(self) -> None:
+        """Raise ``DflError`` (``DFL_ERR_DEVICE_TIMEOUT``) if a bounded device-side wait expired in any layer since the
+        last check.  Synchronises the current stream: for the end of a batch, not for the hot path."""
+
+        if self._status_word is not None:
+            _cabi.check_status(self._status_word)
+
     # ---------------------------------------------------------------- forward
-    def _validate_forward(self, hidden_states, attention_mask, output_attentions, query_states, relative_pos):
-        if self.training:
-            raise RuntimeError("DebertaV2InferenceEncoder requires model.eval()")
-        if torch.is_grad_enabled():
-            raise RuntimeError("DebertaV2InferenceEncoder requires torch.no_grad() or inference_mode()")
-        if output_attentions:
-            raise ValueError("output_attentions=True is not supported")
-        if query_states is not None:
-            raise ValueError("query_states/z_steps are not supported by the inference path")
-        if relative_pos is not None:
-            raise ValueError("custom relative_pos is not supported by the inference path")
-        if attention_mask.dim() != 2:
-            raise ValueError("attention_mask must have shape [B, L]")
-        if attention_mask.shape[:2] != hidden_states.shape[:2]:
+    def _validate_forward(self, hidden_states, attention_mask, output_attentions, query_states, relative_pos) -> Plans:
+        refusals = (
+            (self.training, RuntimeError, "DebertaV2InferenceEncoder requires model.eval()"),
+            (torch.is_grad_enabled(), RuntimeError,
+             "DebertaV2InferenceEncoder requires torch.no_grad() or inference_mode()"),
+            (bool(output_attentions), ValueError, "output_attentions=True is not supported"),
+            (query_states is not None, ValueError, "query_states/z_steps are not supported by the inference path"),
+            (relative_pos is not None, ValueError, "custom relative_pos is not supported by the inference path"),
+            (attention_mask.dim() != 2, ValueError, "attention_mask must have shape [B, L]"),
+        )
+        for refused, error, message in refusals:
+            if refused:
+                raise error(message)
+        if tuple(attention_mask.shape) != tuple(hidden_states.shape[:2]):
             raise ValueError("attention_mask and hidden_states must have matching [B, L]")
-        if self._active_plans is None or self._active_sequence_length is None:
+        table = self._buckets
+        if table.active is None:
             raise RuntimeError("call prepare_for_inference() before forward()")
-        if hidden_states.size(1) != self._active_sequence_length:
+        if hidden_states.size(1) != table.active_length:
             raise ValueError(
-                f"active bucket length {self._active_sequence_length} does not match "
+                f"active bucket length {table.active_length} does not match "
                 f"input length {hidden_states.size(1)}; call activate_shape() first"
             )
-        return self._active_plans
+        return table.active
 
     def forward_prepared(self, hidden_states: torch.Tensor, attention_mask: torch.Tensor,
-                         plans: tuple[B200PreparedPositionPlan, ...], *, output_hidden_states: bool = True,
-                         return_dict: bool = True) -> Any:
+                         plans: Plans, *, output_hidden_states: bool = True, return_dict: bool = True) -> Any:
         """Layer loop with the 2-D mask and prepared plans."""
 
-        all_hidden_states = (hidden_states,) if output_hidden_states else None
-        next_kv = hidden_states
-        input_mask = attention_mask
-        # One dtype conversion per forward instead of one per layer: the kernel
-        # reads bool / integer masks directly.
-        kernel_mask = attention_mask
-        if attention_mask.dtype.is_floating_point:
-            kernel_mask = attention_mask.bool()
-        output_states = hidden_states
-        for index, (layer, plan) in enumerate(zip(self.layer, plans)):
-            self_output, _ = layer.attention.self.forward_prepared(next_kv, kernel_mask, plan)
-            attention_output = layer.attention.output(self_output, next_kv)
-            intermediate_output = layer.intermediate(attention_output)
-            output_states = layer.output(intermediate_output, attention_output)
-            if index == 0 and self.conv is not None:
-                output_states = self.conv(hidden_states, output_states, input_mask)
-            if output_hidden_states:
-                all_hidden_states = all_hidden_states + (output_states,)
-            next_kv = output_states
-
-        if not return_dict:
-            return tuple(v for v in (output_states, all_hidden_states, None) if v is not None)
-        return BaseModelOutput(last_hidden_state=output_states, hidden_states=all_hidden_states, attentions=None)
+        # The kernels test bool / integer mask elements for non-zero themselves; a floating-point mask is turned
+        # into bool here, once per forward and not once per layer.
+        keep = attention_mask.bool() if attention_mask.dtype.is_floating_point else attention_mask
+        trace = [hidden_states] if output_hidden_states else None
+        state = hidden_states
+        for depth, layer in enumerate(self.layer):
+            context, _ = layer.attention.self.forward_prepared(state, keep, plans[depth])
+            mixed = layer.attention.output(context, state)
+            state = layer.output(layer.intermediate(mixed), mixed)
+            if depth == 0 and self.conv is not None:
+                # the convolution branch sees the encoder input and the padding mask as the caller gave it
+                state = self.conv(hidden_states, state, attention_mask)
+            if trace is not None:
+                trace.append(state)
+        collected = None if trace is None else tuple(trace)
+        if return_dict:
+            return BaseModelOutput(last_hidden_state=state, hidden_states=collected, attentions=None)
+        return (state,) if collected is None else (state, collected)
 
     def forward(self, hidden_states: torch.Tensor, attention_mask: torch.Tensor, output_hidden_states: bool = True,
                 output_attentions: bool = False, query_states: torch.Tensor | None = None,
@@ -266,18 +320,18 @@ def enable_deberta_inference(model: nn.Module, *, backend: str = "b200",
     (``deberta.py:313-346``).
     """
 
-    if not hasattr(model, "encoder") or not hasattr(model, "embeddings"):
+    if not (hasattr(model, "encoder") and hasattr(model, "embeddings")):
         raise TypeError("model must be a Hugging Face DeBERTa-v2/v3 backbone")
     if getattr(model, "z_steps", 0) > 1:
         raise ValueError("DeBERTa z_steps > 1 is not supported by the inference path")
     if isinstance(model.encoder, DebertaV2InferenceEncoder):
         raise TypeError("the model already uses DebertaV2InferenceEncoder")
-    was_training = model.training
-    if sequence_lengths is not None and was_training:
+    training = model.training
+    if training and sequence_lengths is not None:
         raise RuntimeError("call model.eval() before preparing inference buckets")
     model.encoder = DebertaV2InferenceEncoder(model.encoder, model.config, backend=backend,
                                               fp32_precision=fp32_precision)
-    model.train(was_training)
+    model.train(training)   # the new sub-modules follow the model's mode
     if sequence_lengths is not None:
         model.encoder.prepare_for_inference(sequence_lengths)
     return model
@@ -291,6 +345,21 @@ def optimize_deberta(model: nn.Module, *, sequence_lengths: Iterable[int] | int 
                                     fp32_precision=fp32_precision)
 
 
+_BUCKET_SOURCE = (
+    "def deberta_bucket_{length}(hidden_states, attention_mask):\n"
+    "    return _layers(hidden_states, attention_mask, _plans, output_hidden_states=False).last_hidden_state\n"
+)
+
+
+def _bucket_function(encoder: DebertaV2InferenceEncoder, length: int, plans: Plans) -> Callable:
+    """A function of its own per bucket (own code object, so that ``torch.compile`` keeps one recompile budget per
+    bucket), closed over the bucket's plans."""
+
+    scope: dict[str, Any] = {"_layers": encoder.forward_prepared, "_plans": plans}
+    exec(compile(_BUCKET_SOURCE.format(length=length), f"<deberta bucket {length}>", "exec"), scope)  # noqa: S102
+    return scope[f"deberta_bucket_{length}"]
+
+
 def compile_deberta_buckets(
     encoder: DebertaV2InferenceEncoder,
     sequence_lengths: Iterable[int] | None = None,
@@ -300,54 +369,35 @@ def compile_deberta_buckets(
     dynamic_batch: bool = True,
     examples: Mapping[int, tuple[torch.Tensor, torch.Tensor]] | None = None,
 ) -> dict[int, Callable[[torch.Tensor, torch.Tensor], torch.Tensor]]:
-    """One ``torch.compile``-d callable per prepared bucket (reference ``deberta.py:349-427``).
+    """One ``torch.compile``-d callable per prepared bucket (the reference's function of this name,
+    ``deberta.py:349-427``).
 
-    Compilation only concerns the PyTorch modules around the attention; the
-    attention itself is the opaque custom op
-    ``disentangled_flash_b200::attention_forward`` and is never traced into.
+    Compilation concerns the PyTorch modules around the attention only; the attention is the opaque custom op
+    ``disentangled_flash_b200::attention_forward`` and is never traced into.  With ``examples`` every bucket is run
+    once (under ``inference_mode``) so that compilation happens here and not on the first request.
     """
 
-    if sequence_lengths is None:
-        lengths = tuple(sorted(encoder._prepared_plans))
-    else:
-        lengths = tuple(dict.fromkeys(int(length) for length in sequence_lengths))
-    missing = [length for length in lengths if length not in encoder._prepared_plans]
-    if missing:
-        raise ValueError(f"unprepared bucket lengths: {missing}")
-
-    isolate = "isolate_recompiles" in inspect.signature(torch.compile).parameters
-    compiled: dict[int, Callable[[torch.Tensor, torch.Tensor], torch.Tensor]] = {}
-
-    def make_forward(plans):
-        def bucket_forward(hidden_states: torch.Tensor, attention_mask: torch.Tensor) -> torch.Tensor:
-            return encoder.forward_prepared(hidden_states, attention_mask, plans,
-                                            output_hidden_states=False).last_hidden_state
-        return bucket_forward
-
+    table = encoder._buckets
+    lengths = tuple(sorted(table.by_length)) if sequence_lengths is None else table.require(sequence_lengths)
+    programs: dict[int, Callable[[torch.Tensor, torch.Tensor], torch.Tensor]] = {}
     for length in lengths:
-        function = make_forward(encoder._prepared_plans[length])
-        kwargs: dict[str, Any] = {"mode": mode, "fullgraph": fullgraph, "dynamic": dynamic_batch}
-        if isolate:
-            kwargs["isolate_recompiles"] = True
-        else:
-            # Distinct code object per bucket so that buckets do not share one recompile budget.
-            clone = types.FunctionType(function.__code__.replace(), function.__globals__,
-                                       name=f"deberta_bucket_{length}", argdefs=function.__defaults__,
-                                       closure=function.__closure__)
-            clone.__kwdefaults__ = function.__kwdefaults__
-            function = clone
-        compiled[length] = torch.compile(function, **kwargs)
-
+        function = _bucket_function(encoder, length, table.by_length[length])
+        options: dict[str, Any] = {"mode": mode, "fullgraph": fullgraph, "dynamic": dynamic_batch}
+        try:   # newer PyTorch can keep recompiles of different callables apart by itself
+            programs[length] = torch.compile(function, isolate_recompiles=True, **options)
+        except TypeError:
+            programs[length] = torch.compile(function, **options)
     if examples is not None:
+        for length in lengths:
+            if length not in examples:
+                raise ValueError(f"missing compilation example for bucket {length}")
+            hidden_states, attention_mask = examples[length]
+            if hidden_states.size(1) != length:
+                raise ValueError(f"bucket {length} example has sequence length {hidden_states.size(1)}")
         with torch.inference_mode():
-            for length, function in compiled.items():
-                if length not in examples:
-                    raise ValueError(f"missing compilation example for bucket {length}")
-                hidden_states, attention_mask = examples[length]
-                if hidden_states.size(1) != length:
-                    raise ValueError(f"bucket {length} example has sequence length {hidden_states.size(1)}")
-                function(hidden_states, attention_mask)
-    return compiled
+            for length in lengths:
+                programs[length](*examples[length])
+    return programs
 
 
 enable_deberta_v2_inference = enable_deberta_inference

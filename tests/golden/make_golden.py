@@ -5,8 +5,9 @@ Run once, in a checkout where the reference sources are available:
     python tests/golden/make_golden.py --reference /path/to/disentangled-flash/src
 
 It imports the reference package (CPU, fp32), runs its own
-``make_log_bucket_position`` / ``SharedPositionPlanCache.compact`` and its
-``original`` and ``torch`` attention backends on seeded inputs, and stores
+``make_log_bucket_position`` / ``SharedPositionPlanCache.compact``, its
+``original`` and ``torch`` attention backends and its ``DebertaV2Encoder``
+(three layers with the layer-0 convolution) on seeded inputs, and stores
 inputs and outputs as ``.npz`` files.  The committed ``.npz`` files are what
 the test-suite reads; this script is never imported by it.
 """
@@ -149,9 +150,47 @@ def generate_attention(ref) -> None:
         print(f"attention_{name}.npz: ctx {tuple(ctx_torch.shape)}, original-vs-torch max abs {diff:.2e}")
 
 
+ENCODER_CASE = dict(hidden=64, heads=2, d=32, layers=3, inter=128, buckets=32, max_pos=64, conv=3,
+                    B=2, L=40, mask="right", seed=201, std=0.08)
+
+
+def generate_encoder(ref) -> None:
+    """Three-layer encoder of the reference (``_reference.py:569-698``) with conv and layer-normed rel embeddings."""
+
+    c = ENCODER_CASE
+    gen = torch.Generator().manual_seed(c["seed"])
+    config = ref._reference.DebertaAttentionConfig(
+        hidden_size=c["hidden"], num_attention_heads=c["heads"], attention_head_size=c["d"],
+        num_hidden_layers=c["layers"], intermediate_size=c["inter"], attention_probs_dropout_prob=0.0,
+        hidden_dropout_prob=0.0, relative_attention=True, max_relative_positions=-1,
+        max_position_embeddings=c["max_pos"], position_buckets=c["buckets"], share_att_key=True,
+        pos_att_type=("p2c", "c2p"), norm_rel_ebd="layer_norm", conv_kernel_size=c["conv"],
+    )
+    encoder = ref._reference.DebertaV2Encoder(config).eval()
+    with torch.no_grad():
+        for name, p in encoder.named_parameters():
+            if name.endswith("LayerNorm.weight"):
+                p.fill_(1.0).add_(torch.randn(p.shape, generator=gen) * 0.05)
+            else:
+                p.normal_(0.0, c["std"], generator=gen)
+    hidden = torch.randn(c["B"], c["L"], c["hidden"], generator=gen)
+    mask = make_mask(c["mask"], c["B"], c["L"], gen)
+    with torch.no_grad():
+        out = encoder(hidden, mask.long(), output_hidden_states=True)
+    arrays = {f"param/{k}": v.detach().numpy() for k, v in encoder.state_dict().items()}
+    arrays.update(hidden=hidden.numpy(), mask=mask.numpy(), last_hidden_state=out.last_hidden_state.numpy(),
+                  layer1=out.hidden_states[1].numpy(),
+                  meta=np.array([c["hidden"], c["heads"], c["d"], c["layers"], c["inter"], c["buckets"],
+                                 c["max_pos"], c["conv"]], dtype=np.int64))
+    np.savez_compressed(HERE / "encoder_conv_L40.npz", **arrays)
+    print("encoder_conv_L40.npz:", tuple(out.last_hidden_state.shape), len(arrays), "arrays")
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--reference", required=True, help="path to the reference's src/ directory")
+    parser.add_argument("--only", choices=("positions", "attention", "encoder"), default=None,
+                        help="regenerate one family of fixtures only")
     args = parser.parse_args()
     sys.path.insert(0, args.reference)
     import disentangled_flash as ref  # noqa: PLC0415
@@ -160,8 +199,13 @@ def main() -> None:
     import disentangled_flash.position  # noqa: F401,PLC0415
 
     torch.manual_seed(0)
-    generate_positions(ref)
-    generate_attention(ref)
+    parser_only = args.only
+    if parser_only in (None, "positions"):
+        generate_positions(ref)
+    if parser_only in (None, "attention"):
+        generate_attention(ref)
+    if parser_only in (None, "encoder"):
+        generate_encoder(ref)
 
 
 if __name__ == "__main__":
