@@ -289,6 +289,48 @@ def test_module_matches_oracle_low_precision(name, dtype_name):
     assert (err <= bound).all(), f"{name} {dtype_name}: max err {err.max().item():.3e}"
 
 
+@pytest.mark.parametrize("name", ATTENTION_GOLDEN)
+@pytest.mark.parametrize("dtype_name", ("fp16", "bf16"))
+def test_module_low_precision_on_the_unscaled_golden_inputs(name, dtype_name):
+    # The same comparison on the fixtures exactly as the reference produced them.  Seven of the eight fixtures were
+    # drawn with std-0.3 weights, which drives scores to +-100: there the softmax is a near one-hot over a few keys
+    # and one 16-bit position score that rounds the other way flips which key wins, in any implementation, so no
+    # useful elementwise bound exists (the test above pins the kernels at a third of the scale).  What can be
+    # required of a correct kernel here: finite outputs, most elements within the standard bound, and an error
+    # that stays within the spread of the values themselves.  The measured errors go into the parity report.
+    import json
+    import os
+
+    from test_oracle_attention import run_oracle
+
+    dtype = DTYPES[dtype_name]
+    g = load_attention_golden(name)
+    g16 = dict(g, params={k: v.to(dtype).float() for k, v in g["params"].items()},
+               hidden_states=g["hidden_states"].to(dtype).float(), rel_embeddings=g["rel_embeddings"].to(dtype).float())
+    want = run_oracle(g16, storage_dtype=dtype)
+    module = build_module(g, dtype)
+    with torch.no_grad():
+        out, _ = module(g["hidden_states"].to(dev, dtype), g["mask"].to(dev), rel_embeddings=g["rel_embeddings"].to(dev, dtype))
+    got = out.float().cpu()
+    assert torch.isfinite(got).all()
+    err = (got - want).abs()
+    ulp = 2.0 ** -11 if dtype == torch.float16 else 2.0 ** -8
+    bound = 2e-3 + want.abs() * ulp
+    within = (err <= bound).float().mean().item()
+    record = {"max_abs_err": err.max().item(), "max_err_in_output_ulps": (err / (want.abs() * ulp + 1e-30)).clamp(max=1e6).max().item(),
+              "fraction_within_standard_bound": within, "max_abs_ref": want.abs().max().item(),
+              "within_bare_2e-3": bool((err <= 2e-3).all())}
+    path = os.environ.get("DFL_PARITY_REPORT_GOLDEN")
+    if path:
+        table = json.load(open(path)) if os.path.exists(path) else {}
+        table[f"golden {name} {dtype_name} unscaled"] = record
+        json.dump(table, open(path, "w"), indent=1, sort_keys=True)
+    # measured on a B200: FP16 max 2e-3 .. 4.5e-3 with >= 99.97 % of the elements inside the standard bound; BF16 max
+    # 2.6e-3 .. 3.0e-2 with >= 99.5 %; outputs reach +-11
+    cap = 1e-2 if dtype == torch.float16 else 5e-2
+    assert within >= 0.99 and err.max().item() <= cap, (name, dtype_name, record)
+
+
 def test_reference_fused_qkv_pins():
     # reference tests/test_fused_qkv.py:7-30 (shapes differ only in being head-major)
     import disentangled_flash_b200 as df
