@@ -58,8 +58,8 @@ MIXED = dict(name="deberta-v3-large-mixed-buckets", geometry="v3-large", buckets
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
 # DRAM bytes of one dfl_attention_rel_fwd launch per sequence of the default workload (12 heads, L=512, d=64, FP16,
 # valid lengths U[256,512]): dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture summarised in
-# profiles/attention_rel_kernel_v3base_fp16.md, divided by the batch of that capture.
-ATTN_DRAM_BYTES_PER_SEQUENCE = None
+# profiles/attention_rel_kernel_v3base_b32_l512_d64_fp16.md (81.1 MB read + 12.5 MB written at B=32), per sequence.
+ATTN_DRAM_BYTES_PER_SEQUENCE = (81.146624e6 + 12.506368e6) / 32
 
 
 def make_config(geometry: str, layers: int | None = None):
