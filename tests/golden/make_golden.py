@@ -48,6 +48,10 @@ ATTENTION_CASES = {
                                 share=True, rel=True, B=2, L=130, mask="all", seed=105),
     "norel_L20_right": dict(hidden=64, heads=2, d=32, buckets=32, max_pos=64, types=(),
                             share=True, rel=False, B=2, L=20, mask="right", seed=106),
+    # relative attention off with both position types still configured: the scale stays 1/sqrt(3d) in the
+    # HF-equivalent backends (_reference.py:277-286), where the Triton module would use 1/sqrt(d) (kernel.py:587)
+    "norel_c2p_p2c_L20_right": dict(hidden=64, heads=2, d=32, buckets=32, max_pos=64, types=("c2p", "p2c"),
+                                    share=True, rel=False, B=2, L=20, mask="right", seed=109),
     "nobucket_L24_none": dict(hidden=64, heads=2, d=32, buckets=-1, max_pos=32, types=("p2c", "c2p"),
                               share=True, rel=True, B=2, L=24, mask="none", seed=107),
     "b256_d64_L160": dict(hidden=128, heads=2, d=64, buckets=256, max_pos=512, types=("p2c", "c2p"),
@@ -98,9 +102,11 @@ def generate_positions(ref) -> None:
     print("position_plans.npz:", len(out), "arrays")
 
 
-def generate_attention(ref) -> None:
+def generate_attention(ref, names=None) -> None:
     cfg_cls = ref._reference.DebertaAttentionConfig
     for name, c in ATTENTION_CASES.items():
+        if names and name not in names:
+            continue
         gen = torch.Generator().manual_seed(c["seed"])
         config = cfg_cls(
             hidden_size=c["hidden"], num_attention_heads=c["heads"], attention_head_size=c["d"],
@@ -191,6 +197,8 @@ def main() -> None:
     parser.add_argument("--reference", required=True, help="path to the reference's src/ directory")
     parser.add_argument("--only", choices=("positions", "attention", "encoder"), default=None,
                         help="regenerate one family of fixtures only")
+    parser.add_argument("--case", action="append", default=None,
+                        help="with --only attention: regenerate only the named case(s)")
     args = parser.parse_args()
     sys.path.insert(0, args.reference)
     import disentangled_flash as ref  # noqa: PLC0415
@@ -203,7 +211,7 @@ def main() -> None:
     if parser_only in (None, "positions"):
         generate_positions(ref)
     if parser_only in (None, "attention"):
-        generate_attention(ref)
+        generate_attention(ref, args.case)
     if parser_only in (None, "encoder"):
         generate_encoder(ref)
 
