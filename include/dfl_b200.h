@@ -233,7 +233,7 @@ DFL_API size_t dfl_static_scratch_bytes(void);
  * rounded to the input type as the separate score GEMMs round their output, scale, 2-D padding mask,
  * softmax, PV.  The score tensors [B,H,L,A] never exist in global memory.  A persistent kernel: one CTA
  * per SM walks (batch, head, 128-query-tile) items.  Covered: FP16/BF16, head_dim 32 or 64, at least one
- * relative term, seq_len <= 1024; dfl_attention_rel_supported() tells, other configurations return
+ * relative term, seq_len <= 2048; dfl_attention_rel_supported() tells, other configurations return
  * DFL_ERR_UNSUPPORTED (use dfl_pos_scores + dfl_attention_fwd for them).
  */
 typedef struct DflAttnRelParams {
