@@ -39,6 +39,8 @@ EXPORTED_SYMBOLS = (
     "dfl_build_position_lut",
     "dfl_qkv_proj",
     "dfl_gather_slots",
+    "dfl_add_layernorm",
+    "dfl_add_layernorm_supported",
     "dfl_pos_scores",
     "dfl_attention_fwd",
     "dfl_attention_fwd_static",
@@ -95,6 +97,11 @@ class DflAttnRelParams(Structure):
     ]
 
 
+class DflAddLayerNormParams(Structure):
+    _fields_ = [("x", c_void_p), ("residual", c_void_p), ("gamma", c_void_p), ("beta", c_void_p), ("out", c_void_p),
+                ("rows", ctypes.c_int64), ("hidden", c_int), ("eps", ctypes.c_float), ("dtype", c_int)]
+
+
 class DflError(RuntimeError):
     """A C entry point returned a negative status."""
 
@@ -129,6 +136,10 @@ def load_library() -> ctypes.CDLL:
     lib.dfl_build_position_lut.argtypes = [c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.dfl_qkv_proj.restype = c_int
     lib.dfl_qkv_proj.argtypes = [POINTER(DflLinearParams), c_void_p]
+    lib.dfl_add_layernorm_supported.restype = c_int
+    lib.dfl_add_layernorm_supported.argtypes = [c_int, c_int]
+    lib.dfl_add_layernorm.restype = c_int
+    lib.dfl_add_layernorm.argtypes = [POINTER(DflAddLayerNormParams), c_void_p]
     lib.dfl_gather_slots.restype = c_int
     lib.dfl_gather_slots.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
     lib.dfl_pos_scores.restype = c_int
@@ -266,6 +277,40 @@ def gather_slots(src: torch.Tensor, active: torch.Tensor) -> torch.Tensor:
         _check(lib.dfl_gather_slots(src.data_ptr(), active.data_ptr(), dst.data_ptr(), heads, n_src, n_active, d,
                                     dtype_code(src.dtype), _stream(src.device)), "dfl_gather_slots")
     return dst
+
+
+def add_layernorm_supported(dtype: torch.dtype, hidden: int) -> bool:
+    """Whether ``add_layernorm`` covers rows of ``hidden`` elements of this type."""
+
+    if dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        return False
+    return bool(load_library().dfl_add_layernorm_supported(dtype_code(dtype), int(hidden)))
+
+
+def add_layernorm(x: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor | None,
+                  eps: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``LayerNorm(x + residual) * weight + bias`` over the last dimension, sum and statistics in fp32."""
+
+    lib = load_library()
+    hidden = x.shape[-1]
+    for name, t in (("x", x), ("residual", residual), ("weight", weight), ("bias", bias)):
+        if t is None:
+            continue
+        _require_cuda_contiguous(name, t)
+        if t.dtype != x.dtype:
+            raise TypeError(f"{name} must have the dtype of x ({x.dtype}), got {t.dtype}")
+    if residual is not None and residual.shape != x.shape:
+        raise ValueError("residual must have the shape of x")
+    if weight.numel() != hidden or (bias is not None and bias.numel() != hidden):
+        raise ValueError("weight and bias must have one element per column of x")
+    if out is None:
+        out = torch.empty_like(x)
+    p = DflAddLayerNormParams()
+    p.x, p.residual, p.gamma, p.beta, p.out = _ptr(x), _ptr(residual), _ptr(weight), _ptr(bias), _ptr(out)
+    p.rows, p.hidden, p.eps, p.dtype = x.numel() // hidden, hidden, float(eps), dtype_code(x.dtype)
+    with torch.cuda.device(x.device):
+        _check(lib.dfl_add_layernorm(ctypes.byref(p), _stream(x.device)), "dfl_add_layernorm")
+    return out
 
 
 def padded_slots(n_active: int) -> int:

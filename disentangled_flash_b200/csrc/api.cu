@@ -175,6 +175,28 @@ int dfl_expand_rel_tables(const void* pos, const int32_t* lut_dev, void* rel, in
   return launch_expand_rel_tables(pos, lut_dev, rel, heads, n_active, seq_len, head_dim, dtype, (cudaStream_t)stream);
 }
 
+int dfl_add_layernorm_supported(int dtype, int hidden) {
+  if (!valid_dtype(dtype) || hidden < 1) return 0;
+  const int elems = (int)(16 / dtype_size(dtype));
+  return hidden % elems == 0 && hidden <= add_layernorm_max_hidden(dtype_size(dtype)) ? 1 : 0;
+}
+
+int dfl_add_layernorm(const DflAddLayerNormParams* p, void* stream) {
+  if (!p) return fail(DFL_ERR_BAD_ARG, "null params");
+  if (!valid_dtype(p->dtype)) return fail(DFL_ERR_BAD_ARG, "unknown dtype %d", p->dtype);
+  if (p->rows < 0 || p->hidden < 1) return fail(DFL_ERR_BAD_ARG, "non-positive size");
+  if (!(p->eps >= 0.0f)) return fail(DFL_ERR_BAD_ARG, "eps must be non-negative");
+  if (!dfl_add_layernorm_supported(p->dtype, p->hidden))
+    return fail(DFL_ERR_UNSUPPORTED, "hidden size %d: rows must be multiples of 16 bytes and at most %d elements",
+                p->hidden, add_layernorm_max_hidden(dtype_size(p->dtype)));
+  if (p->rows == 0) return DFL_OK;
+  if (!p->x || !p->gamma || !p->out) return fail(DFL_ERR_BAD_ARG, "null pointer");
+  if (!aligned16(p->x) || !aligned16(p->residual) || !aligned16(p->gamma) || !aligned16(p->beta) || !aligned16(p->out))
+    return fail(DFL_ERR_ALIGNMENT, "pointers must be 16-byte aligned");
+  return launch_add_layernorm(p->x, p->residual, p->gamma, p->beta, p->out, p->rows, p->hidden, p->eps, p->dtype,
+                              (cudaStream_t)stream);
+}
+
 int dfl_attention_rel_supported(const DflAttnRelParams* p) {
   return p && p->algo == DFL_ALGO_AUTO && attention_rel_supported(*p) ? 1 : 0;
 }

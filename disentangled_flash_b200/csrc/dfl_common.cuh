@@ -136,6 +136,9 @@ int launch_attention_simt(const DflAttnParams& p, cudaStream_t stream);
 int launch_attention_tc(const DflAttnParams& p, cudaStream_t stream);
 bool attention_rel_supported(const DflAttnRelParams& p);
 int launch_attention_rel(const DflAttnRelParams& p, cudaStream_t stream);
+int add_layernorm_max_hidden(size_t elem_size);
+int launch_add_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* out,
+                         long long rows, int hidden, float eps, int dtype, cudaStream_t stream);
 int launch_selftest_bounded_wait(int* status, uint32_t limit_us, cudaStream_t stream);
 int launch_expand_rel_tables(const void* pos, const int32_t* lut, void* rel, int heads, int n_active, int seq_len,
                              int head_dim, int dtype, cudaStream_t stream);

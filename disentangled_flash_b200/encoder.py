@@ -13,8 +13,11 @@ tuple of per-layer position plans (a ``_BucketTable``); a forward pass walks the
 layers with the 2-D padding mask and the active tuple.  No ``[B,1,L,L]`` mask
 and no ``[L,L]`` relative-position tensor exists at any point.
 
-Everything outside ``attention.self`` (attention output projection, FFN, layer
-norms, the layer-0 convolution) stays ordinary PyTorch.  There is one backend;
+Outside ``attention.self`` the dense projections, the activation and the
+layer-0 convolution stay the caller's PyTorch modules; the tail of the two
+output blocks of a layer, ``LayerNorm(dense(x) + residual)``, runs the add and
+the norm as one kernel (``dfl_add_layernorm``) when the block has the Hugging
+Face shape (``dense`` / ``LayerNorm`` / ``dropout``).  There is one backend;
 ``backend="triton"`` is accepted as the legacy name of the fused backend and
 ``backend="torch"`` is refused because no CPU/PyTorch attention ships here.
 """
@@ -23,10 +26,11 @@ from __future__ import annotations
 
 from collections.abc import Callable, Iterable, Mapping
 from dataclasses import dataclass
-from typing import Any
+from typing import Any, Optional
 
 import torch
 from torch import nn
+from torch.nn import functional as F
 
 from . import _cabi
 from .attention import B200PreparedPositionPlan, DisentangledFlashAttention
@@ -50,6 +54,48 @@ class BaseModelOutput:
     def __getitem__(self, index: int) -> Any:
         fields = (self.last_hidden_state, self.hidden_states, self.attentions)
         return [field for field in fields if field is not None][index]
+
+
+@torch.library.custom_op("disentangled_flash_b200::add_layernorm", mutates_args=(), device_types="cuda")
+def _add_layernorm_op(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                      eps: float) -> torch.Tensor:
+    """``LayerNorm(x + residual)`` in one pass; sum and statistics in fp32 (``dfl_add_layernorm``)."""
+
+    return _cabi.add_layernorm(x.contiguous(), residual.contiguous(), weight, bias, eps)
+
+
+@_add_layernorm_op.register_fake
+def _add_layernorm_fake(x, residual, weight, bias, eps):
+    return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+
+_OUTPUT_BLOCK_CHILDREN = frozenset(("dense", "LayerNorm", "dropout"))
+
+
+def _output_block_is_fusable(block: nn.Module) -> bool:
+    """Whether ``block`` is ``LayerNorm(dropout(dense(x)) + residual)`` in the Hugging Face shape
+    (``_reference.py:101-112``, ``474-485``) at a size and type ``dfl_add_layernorm`` covers.  Decided when a bucket
+    is prepared, not in the forward pass."""
+
+    dense, norm = getattr(block, "dense", None), getattr(block, "LayerNorm", None)
+    if not (isinstance(dense, nn.Linear) and isinstance(norm, nn.LayerNorm) and norm.weight is not None):
+        return False
+    if not {name for name, _ in block.named_children()} <= _OUTPUT_BLOCK_CHILDREN:
+        return False
+    weight = norm.weight
+    return (weight.is_cuda and len(norm.normalized_shape) == 1 and dense.weight.dtype == weight.dtype
+            and _cabi.add_layernorm_supported(weight.dtype, norm.normalized_shape[0]))
+
+
+def _output_block(block: nn.Module, fused: bool, projected: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+    """A layer's output block; with ``fused`` the add and the norm are one kernel (the encoder runs in eval mode,
+    so the block's dropout is the identity)."""
+
+    if not fused or projected.dtype != block.LayerNorm.weight.dtype or residual.dtype != projected.dtype:
+        return block(projected, residual)
+    dense, norm = block.dense, block.LayerNorm
+    return _add_layernorm_op(F.linear(projected, dense.weight, dense.bias), residual, norm.weight, norm.bias,
+                             float(norm.eps))
 
 
 class _BucketTable:
@@ -159,6 +205,7 @@ class DebertaV2InferenceEncoder(nn.Module):
             _adopt_attention(layer, config, self.position_plan_cache, fp32_precision)
 
         self._buckets = _BucketTable()
+        self._fused_output_blocks: list[tuple[bool, bool]] = [(False, False)] * len(self.layer)
         self._status_word: torch.Tensor | None = None
         self.register_load_state_dict_post_hook(_drop_plans_after_load)
 
@@ -238,6 +285,10 @@ class DebertaV2InferenceEncoder(nn.Module):
         for length in lengths:
             self._buckets.by_length[length] = tuple(module.prepare_shape(length, device) for module in modules)
         self._buckets.select(lengths[0])
+        self._fused_output_blocks = [
+            (_output_block_is_fusable(layer.attention.output), _output_block_is_fusable(layer.output))
+            for layer in self.layer
+        ] if device.type == "cuda" else [(False, False)] * len(self.layer)
         return self
 
     def activate_shape(self, sequence_length: int) -> "DebertaV2InferenceEncoder":
@@ -290,8 +341,9 @@ class DebertaV2InferenceEncoder(nn.Module):
         state = hidden_states
         for depth, layer in enumerate(self.layer):
             context, _ = layer.attention.self.forward_prepared(state, keep, plans[depth])
-            mixed = layer.attention.output(context, state)
-            state = layer.output(layer.intermediate(mixed), mixed)
+            fuse_attention_output, fuse_output = self._fused_output_blocks[depth]
+            mixed = _output_block(layer.attention.output, fuse_attention_output, context, state)
+            state = _output_block(layer.output, fuse_output, layer.intermediate(mixed), mixed)
             if depth == 0 and self.conv is not None:
                 # the convolution branch sees the encoder input and the padding mask as the caller gave it
                 state = self.conv(hidden_states, state, attention_mask)

@@ -255,6 +255,32 @@ DFL_API int dfl_expand_rel_tables(const void* pos, const int32_t* lut_dev, void*
 DFL_API int dfl_attention_rel_supported(const DflAttnRelParams* p);
 DFL_API int dfl_attention_rel_fwd(const DflAttnRelParams* p, void* stream);
 
+/*
+ * Residual add + LayerNorm in one pass (the tail of a layer's two output blocks):
+ *     out[r, :] = LayerNorm(x[r, :] + residual[r, :]) * gamma + beta
+ * with the sum, the mean and the (biased) variance in fp32 and the result rounded to `dtype`.  Replaces, in the
+ * encoder's layer loop (deberta.py:268-270), `self.LayerNorm(hidden_states + input_tensor)` of
+ * DebertaV2SelfOutput.forward (_reference.py:108-112) and DebertaV2Output.forward (_reference.py:481-485), which
+ * PyTorch runs as an elementwise add and a layer-norm kernel; the dense projection in front of it stays the
+ * caller's GEMM.  x, residual and out are [rows, hidden] row-major (out may alias x or residual), gamma and beta
+ * [hidden]; residual and beta may be NULL.  hidden * sizeof(dtype) must be a multiple of 16 bytes and hidden at most
+ * 4096 (F16/BF16) or 2048 (F32): dfl_add_layernorm_supported() tells, other sizes return DFL_ERR_UNSUPPORTED.
+ * Unlike PyTorch, which rounds the sum to `dtype` before normalising, the sum stays in fp32.
+ */
+typedef struct DflAddLayerNormParams {
+  const void* x;         /* [rows, hidden] */
+  const void* residual;  /* [rows, hidden] or NULL */
+  const void* gamma;     /* [hidden] */
+  const void* beta;      /* [hidden] or NULL */
+  void*       out;       /* [rows, hidden] */
+  int64_t rows;
+  int32_t hidden;
+  float   eps;
+  int32_t dtype;
+} DflAddLayerNormParams;
+DFL_API int dfl_add_layernorm_supported(int dtype, int hidden);
+DFL_API int dfl_add_layernorm(const DflAddLayerNormParams* p, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
