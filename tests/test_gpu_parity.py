@@ -94,7 +94,8 @@ def test_plan_cache_reference_pins():
 
 # ------------------------------------------------------------------ projections
 @pytest.mark.parametrize("dtype_name,algo", DTYPE_ALGO)
-@pytest.mark.parametrize("shape", [(2, 8, 64, 1, 64), (2, 33, 96, 3, 32), (3, 130, 256, 2, 128), (4, 128, 768, 12, 64)])
+@pytest.mark.parametrize("shape", [(2, 8, 64, 1, 64), (2, 33, 96, 3, 32), (3, 130, 256, 2, 128), (4, 128, 768, 12, 64),
+                                   (160, 256, 128, 2, 64)])   # the last: more 256-row tiles than CTA pairs
 def test_qkv_projection(dtype_name, algo, shape):
     batch, length, hidden, heads, d = shape
     dtype = DTYPES[dtype_name]
