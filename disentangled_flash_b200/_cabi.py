@@ -40,6 +40,7 @@ EXPORTED_SYMBOLS = (
     "dfl_qkv_proj",
     "dfl_gather_slots",
     "dfl_add_layernorm",
+    "dfl_dense",
     "dfl_add_layernorm_supported",
     "dfl_pos_scores",
     "dfl_attention_fwd",
@@ -97,6 +98,15 @@ class DflAttnRelParams(Structure):
     ]
 
 
+class DflDenseParams(Structure):
+    _fields_ = [("x", c_void_p), ("w", c_void_p), ("bias", c_void_p), ("out", c_void_p),
+                ("M", c_int32), ("N", c_int32), ("K", c_int32), ("activation", c_int32), ("dtype", c_int32),
+                ("algo", c_int32), ("status", c_void_p)]
+
+
+ACT_NONE, ACT_GELU = 0, 1
+
+
 class DflAddLayerNormParams(Structure):
     _fields_ = [("x", c_void_p), ("residual", c_void_p), ("gamma", c_void_p), ("beta", c_void_p), ("out", c_void_p),
                 ("rows", ctypes.c_int64), ("hidden", c_int), ("eps", ctypes.c_float), ("dtype", c_int)]
@@ -136,6 +146,8 @@ def load_library() -> ctypes.CDLL:
     lib.dfl_build_position_lut.argtypes = [c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.dfl_qkv_proj.restype = c_int
     lib.dfl_qkv_proj.argtypes = [POINTER(DflLinearParams), c_void_p]
+    lib.dfl_dense.restype = c_int
+    lib.dfl_dense.argtypes = [POINTER(DflDenseParams), c_void_p]
     lib.dfl_add_layernorm_supported.restype = c_int
     lib.dfl_add_layernorm_supported.argtypes = [c_int, c_int]
     lib.dfl_add_layernorm.restype = c_int
@@ -277,6 +289,30 @@ def gather_slots(src: torch.Tensor, active: torch.Tensor) -> torch.Tensor:
         _check(lib.dfl_gather_slots(src.data_ptr(), active.data_ptr(), dst.data_ptr(), heads, n_src, n_active, d,
                                     dtype_code(src.dtype), _stream(src.device)), "dfl_gather_slots")
     return dst
+
+
+def dense(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, *, activation: int = ACT_NONE,
+          algo: int = ALGO_AUTO, status: torch.Tensor | None = None) -> torch.Tensor:
+    """``act(x @ weight^T + bias)`` over the last dimension of ``x`` with bias and activation in the GEMM epilogue."""
+
+    lib = load_library()
+    for name, t in (("x", x), ("weight", weight), ("bias", bias)):
+        if t is None:
+            continue
+        _require_cuda_contiguous(name, t)
+        if t.dtype != x.dtype:
+            raise TypeError(f"{name} must have the dtype of x ({x.dtype}), got {t.dtype}")
+    n, k = weight.shape
+    if x.shape[-1] != k or (bias is not None and bias.numel() != n):
+        raise ValueError("shapes of x, weight and bias do not agree")
+    out = torch.empty(*x.shape[:-1], n, dtype=x.dtype, device=x.device)
+    p = DflDenseParams()
+    p.x, p.w, p.bias, p.out = _ptr(x), _ptr(weight), _ptr(bias), _ptr(out)
+    p.M, p.N, p.K = x.numel() // k, n, k
+    p.activation, p.dtype, p.algo, p.status = activation, dtype_code(x.dtype), algo, _ptr(status)
+    with torch.cuda.device(x.device):
+        _check(lib.dfl_dense(ctypes.byref(p), _stream(x.device)), "dfl_dense")
+    return out
 
 
 def add_layernorm_supported(dtype: torch.dtype, hidden: int) -> bool:

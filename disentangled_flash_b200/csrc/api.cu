@@ -175,6 +175,30 @@ int dfl_expand_rel_tables(const void* pos, const int32_t* lut_dev, void* rel, in
   return launch_expand_rel_tables(pos, lut_dev, rel, heads, n_active, seq_len, head_dim, dtype, (cudaStream_t)stream);
 }
 
+int dfl_dense(const DflDenseParams* p, void* stream) {
+  if (!p) return fail(DFL_ERR_BAD_ARG, "null params");
+  if (!valid_dtype(p->dtype)) return fail(DFL_ERR_BAD_ARG, "unknown dtype %d", p->dtype);
+  if (p->M < 0 || p->N < 1 || p->K < 1) return fail(DFL_ERR_BAD_ARG, "non-positive size");
+  if (p->activation != DFL_ACT_NONE && p->activation != DFL_ACT_GELU)
+    return fail(DFL_ERR_BAD_ARG, "unknown activation %d", p->activation);
+  if (p->M == 0) return DFL_OK;
+  if (!p->x || !p->w || !p->out) return fail(DFL_ERR_BAD_ARG, "null pointer");
+  if ((p->N % 8) || (p->K % 8)) return fail(DFL_ERR_ALIGNMENT, "N and K must be multiples of 8 elements");
+  if (!aligned16(p->x) || !aligned16(p->w) || !aligned16(p->out) || !aligned16(p->bias))
+    return fail(DFL_ERR_ALIGNMENT, "pointers must be 16-byte aligned");
+  GemmDesc g{};
+  g.x = p->x; g.w = p->w; g.bias = p->bias; g.out[0] = p->out;
+  g.M = p->M; g.N = p->N; g.K = p->K;
+  g.batch = 1; g.stride_x = 0; g.stride_w = 0; g.w_mod = 1; g.stride_c = 0;
+  g.ldc = p->N;
+  g.head_split = 0; g.heads = 1; g.head_dim = p->N; g.rows_per_seq = p->M;
+  g.dtype = p->dtype;
+  g.status = p->status;
+  g.activation = p->activation;
+  return use_tensor_cores(p->dtype, p->algo) ? launch_gemm_tc(g, (cudaStream_t)stream)
+                                             : launch_gemm_simt(g, (cudaStream_t)stream);
+}
+
 int dfl_add_layernorm_supported(int dtype, int hidden) {
   if (!valid_dtype(dtype) || hidden < 1) return 0;
   const int elems = (int)(16 / dtype_size(dtype));

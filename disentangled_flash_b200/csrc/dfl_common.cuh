@@ -128,7 +128,30 @@ struct GemmDesc {
   int heads, head_dim, rows_per_seq;
   int dtype;
   int* status;          // device status word of the call, or null (the tcgen05 GEMM then uses the library's word)
+  int activation;       // DFL_ACT_*: applied after the bias (row-major epilogue only)
 };
+
+// GELU, 0.5 x (1 + erf(x / sqrt 2)), for the GEMM epilogues.
+// Exact form (strict FP32 kernels): the CUDA library's erff.
+__device__ __forceinline__ float gelu_erf_exact(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+// Fast form (16-bit outputs): erf by the rational approximation 7.1.26 of Abramowitz & Stegun,
+// erf(z) = 1 - (a1 t + ... + a5 t^5) exp(-z^2), t = 1 / (1 + p z), z >= 0, absolute error below 1.5e-7 - three
+// orders of magnitude under the rounding step of an FP16 or BF16 output - with one approximate reciprocal and one
+// approximate exp2 (relative error ~1e-7 each).
+__device__ __forceinline__ float gelu_erf_fast(float x) {
+  // gelu(x) = max(x, 0) - |x| * q(t) * exp(-z^2),  z = |x| / sqrt 2,  q(t) = 0.5 (a1 t + ... + a5 t^5).
+  // With w = z * sqrt(log2 e): exp(-z^2) = exp2(-w^2) and 1 + p z = 1 + (p / sqrt(log2 e)) w.
+  const float ax = fabsf(x);
+  const float w = ax * 0.84932180028801904f;            // sqrt(log2(e) / 2)
+  float t, e;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.27273748088f, w, 1.0f)));   // p / sqrt(log2 e)
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-w * w));
+  float q = fmaf(0.5307027145f, t, -0.7265760135f);      // a5 / 2, a4 / 2
+  q = fmaf(q, t, 0.7107068705f);                          // a3 / 2
+  q = fmaf(q, t, -0.142248368f);                          // a2 / 2
+  q = fmaf(q, t, 0.127414796f);                           // a1 / 2
+  return fmaf(-(ax * (q * t)), e, fmaxf(x, 0.0f));
+}
 int launch_gemm_simt(const GemmDesc& g, cudaStream_t stream);
 int launch_gemm_tc(const GemmDesc& g, cudaStream_t stream);
 

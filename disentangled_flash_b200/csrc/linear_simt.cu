@@ -112,6 +112,7 @@ gemm_simt_kernel(GemmDesc g) {
         if (n >= g.ldc) continue;
         float v = n < g.N ? acc[i][j] : 0.0f;
         if (bias && n < g.N) v += Elem<T>::to_f(bias[n]);
+        if (g.activation == DFL_ACT_GELU) v = gelu_erf_exact(v);
         T* out = reinterpret_cast<T*>(g.out[0]) + (long long)z * g.stride_c;
         out[(long long)m * g.ldc + n] = Elem<T>::from_f(v);
       }

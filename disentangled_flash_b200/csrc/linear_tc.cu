@@ -9,14 +9,15 @@
 //
 //   C_z[m,n] = sum_k X_z[m,k] * W_{z % w_mod}[n,k] (+ bias[n]),  fp32 accumulation in TMEM
 //
-// Persistent kernel, one CTA per SM, each walking 128x256 output tiles.  Warp 4
-// streams K-blocks of X and W into a 4-stage shared-memory ring with TMA
-// (128-byte swizzle, K-major) and keeps streaming across tile boundaries,
-// warp 5 issues tcgen05.mma (M=128, N=256, K=16) from one elected thread into
-// one of two 256-column TMEM accumulators, warps 0-3 read the finished
-// accumulator back with tcgen05.ld (one row per thread), add the bias, round to
-// the output type and store 64-byte row segments either head-major [B,H,L,d] or
-// row-major -- while the MMA warp already fills the other accumulator.
+// Two kernels, both persistent with one CTA per SM and 320 threads.  A producer warp streams K-blocks of X and W
+// into a shared-memory ring with TMA (128-byte swizzle, K-major) and keeps streaming across tile boundaries, one
+// elected thread of the MMA warp issues tcgen05.mma into one of two 256-column TMEM accumulators, and eight
+// epilogue warps drain the finished accumulator (tcgen05.ld, one row per thread, 128 columns per warp), add the
+// bias, apply the activation, round to the output type, stage 32 x 64 blocks in shared memory and write them with
+// tiled bulk stores, head-major [B,H,L,d] or row-major - while the MMA warp already fills the other accumulator.
+//   * gemm_tc_pair_kernel: clusters of two CTAs on one 256 x 256 tile (cta_group::2), six 32 KB stages per CTA;
+//     used whenever M >= 256 and K >= 64.
+//   * gemm_tc_kernel: one CTA per 128 x 256 tile, for the small shapes.
 #include <cstring>
 
 #include "dfl_common.cuh"
@@ -71,15 +72,18 @@ __device__ int g_gemm_status = 0;
 namespace {
 
 constexpr int TM = 128, TN = 256;  // 128 x 256 output tile: 87 flop per operand byte staged through shared memory
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 8;   // warp w drains TMEM lanes 32*(w&3).. of accumulator columns 128*(w>>2)..
+constexpr int kTmaWarp = 8, kMmaWarp = 9;
+constexpr int kThreads = 320;
 constexpr int kTmemCols = 512;      // two 256-column accumulators: epilogue of tile i overlaps main loop of tile i+1
 constexpr int kMaxSmem = 232448;
 
-// Output staging for the tiled-store epilogue: per epilogue warp two buffers of 32 rows x 64 columns (128-byte
-// rows in the 128-byte swizzle pattern of the output tensor maps).
+// Output staging for the tiled-store epilogue: per epilogue warp one buffer of 32 rows x 64 columns (128-byte
+// rows in the 128-byte swizzle pattern of the output tensor maps).  Two warps share a scheduler, so one converts
+// while the other's store drains its buffer.
 constexpr int kStageRows = 32, kStageCols = 64;
 constexpr int kStageBufBytes = kStageRows * kStageCols * 2;   // 4 KB
-constexpr int kStagingBytes = 4 * 2 * kStageBufBytes;          // 4 warps x 2 buffers = 32 KB
+constexpr int kStagingBytes = 8 * kStageBufBytes;              // one buffer per epilogue warp = 32 KB
 
 struct OutMaps {
   CUtensorMap m[3];
@@ -126,6 +130,10 @@ __device__ __forceinline__ void store_chunk(const GemmDesc& g, const uint32_t (&
 #pragma unroll
       for (int j = 0; j < 8; ++j) f[j] += Elem<T>::to_f(bh[j]);
     }
+    if (g.activation == DFL_ACT_GELU) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = gelu_erf_fast(f[j]);
+    }
     uint4 packed;
     T* ph = reinterpret_cast<T*>(&packed);
 #pragma unroll
@@ -140,22 +148,23 @@ __host__ __device__ inline bool tiled_store_ok(const GemmDesc& g) {
   return !g.head_split || (g.head_dim % kStageCols == 0 && g.rows_per_seq % kStageRows == 0);
 }
 
-// Drains one warp's 32 lanes x 256 columns of an accumulator.  `taddr` = TMEM address of the warp's lane quarter at
-// the accumulator's first column, `m_warp` = output row of lane 0, `n0` = first output column.
+// Drains one warp's 32 lanes x 128 columns of an accumulator.  `taddr` = TMEM address of the warp's lane quarter at
+// the accumulator's first column, `m_warp` = output row of lane 0, `n0` = first output column of the tile,
+// `col_begin` = first accumulator column of this warp (0 or 128).
 // With `tiled` the rows go through the warp's staging buffers and leave as tiled bulk stores of full 128-byte
 // lines (per-thread stores would write every 32-byte sector in two halves from different instructions, and the
 // number of store requests, not the math, then bounds GEMMs with a short K).
 template <typename T>
 __device__ __forceinline__ void drain_accumulator(const GemmDesc& g, const CUtensorMap* tmap_out, bool tiled,
-                                                  unsigned char* staging, uint32_t& groups, uint32_t taddr,
-                                                  int m_warp, int n0, int z, bool ready, int lane) {
+                                                  unsigned char* buf, uint32_t taddr, int m_warp, int n0,
+                                                  int col_begin, int z, bool ready, int lane) {
   const int ncols = g.head_split ? g.N : g.ldc;
   const T* bias = reinterpret_cast<const T*>(g.bias);
   const int hd = g.heads * g.head_dim;
   if (!tiled) {
     const int m = m_warp + lane;
 #pragma unroll 1
-    for (int c0 = 0; c0 < TN; c0 += 32) {
+    for (int c0 = col_begin; c0 < col_begin + TN / 2; c0 += 32) {
       const int n = n0 + c0;
       if (n >= ncols) break;  // warp-uniform
       uint32_t r[32];
@@ -167,15 +176,14 @@ __device__ __forceinline__ void drain_accumulator(const GemmDesc& g, const CUten
     return;
   }
 #pragma unroll 1
-  for (int c0 = 0; c0 < TN; c0 += kStageCols) {
+  for (int c0 = col_begin; c0 < col_begin + TN / 2; c0 += kStageCols) {
     const int n = n0 + c0;
     if (n >= ncols) break;  // warp-uniform
-    unsigned char* buf = staging + (groups & 1u) * kStageBufBytes;
     uint32_t r0[32], r1[32];
     ptx::tmem_ld32(taddr + (uint32_t)c0, r0);
     ptx::tmem_ld32(taddr + (uint32_t)c0 + 32u, r1);
-    // the store that last read this buffer (two groups ago) has finished reading it
-    if (lane == 0) ptx::bulk_wait_group_read<1>();
+    // the previous store of this warp has finished reading the buffer
+    if (lane == 0) ptx::bulk_wait_group_read<0>();
     __syncwarp();
     ptx::tmem_wait_ld();
     if (!ready || m_warp >= g.M) continue;  // warp-uniform
@@ -189,6 +197,10 @@ __device__ __forceinline__ void drain_accumulator(const GemmDesc& g, const CUten
         const T* bh = reinterpret_cast<const T*>(&braw);
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] += Elem<T>::to_f(bh[j]);
+      }
+      if (g.activation == DFL_ACT_GELU) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = gelu_erf_fast(f[j]);
       }
       uint4 packed;
       T* ph = reinterpret_cast<T*>(&packed);
@@ -209,7 +221,6 @@ __device__ __forceinline__ void drain_accumulator(const GemmDesc& g, const CUten
       }
       ptx::bulk_commit_group();
     }
-    ++groups;
   }
 }
 
@@ -240,16 +251,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(&tmem_full_bar[a], 1);
-      ptx::mbar_init(&tmem_empty_bar[a], 4);  // one elected lane of each epilogue warp
+      ptx::mbar_init(&tmem_empty_bar[a], kEpilogueWarps);  // one elected lane of each epilogue warp
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == kTmaWarp && lane == 0) {
     ptx::prefetch_tensormap(&tmap_x);
     ptx::prefetch_tensormap(&tmap_w);
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     ptx::tmem_alloc(tmem_holder, kTmemCols);
     ptx::tmem_relinquish();
   }
@@ -267,7 +278,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     n0 = (rem - tm * tiles_n) * TN;
   };
 
-  if (warp == 4) {
+  if (warp == kTmaWarp) {
     // ---------------------------------------------------------- TMA producer
     if (lane == 0) {
       uint32_t it = 0;
@@ -287,7 +298,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = ptx::make_idesc_f16(__is_same(T, __nv_bfloat16) ? 1 : 0, TM, TN, 0, 0);
@@ -323,8 +334,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     }
   } else {
     // -------------------------------------------------------------- epilogue
-    unsigned char* staging = smem + S::kStagingOffset + warp * 2 * kStageBufBytes;
-    uint32_t groups = 0;
+    unsigned char* staging = smem + S::kStagingOffset + warp * kStageBufBytes;
+    const int quarter = warp & 3, col_begin = (warp >> 2) * (TN / 2);
     bool ready = true;
     int lt = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++lt) {
@@ -333,9 +344,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
       const int acc = lt & 1;
       if (ready) ready = ptx::mbar_wait(&tmem_full_bar[acc], (uint32_t)(lt >> 1) & 1u, abort_flag, g.status, 3);
       ptx::tc_fence_after();
-      drain_accumulator<T>(g, tmap_out.m, tiled != 0, staging, groups,
-                           tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * TN), m0 + warp * 32, n0, z,
-                           ready, lane);
+      drain_accumulator<T>(g, tmap_out.m, tiled != 0, staging,
+                           tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * TN), m0 + quarter * 32, n0,
+                           col_begin, z, ready, lane);
       // this warp has read its lanes of the accumulator: hand it back to the MMA issuer
       ptx::tc_fence_before();
       __syncwarp();
@@ -346,7 +357,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
 
   ptx::tc_fence_before();
   __syncthreads();
-  if (warp == 5) ptx::tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == kMmaWarp) ptx::tmem_dealloc(tmem_base, kTmemCols);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -393,16 +404,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(&tmem_full_bar[a], 1);
-      ptx::mbar_init(&tmem_empty_bar[a], 8);  // one elected lane of each epilogue warp of both CTAs (leader's only)
+      ptx::mbar_init(&tmem_empty_bar[a], 2 * kEpilogueWarps);  // one lane of each epilogue warp of both CTAs (leader's only)
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == kTmaWarp && lane == 0) {
     ptx::prefetch_tensormap(&tmap_x);
     ptx::prefetch_tensormap(&tmap_w);
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     ptx::tmem_alloc_pair(tmem_holder, kTmemCols);
     ptx::tmem_relinquish_pair();
   }
@@ -421,7 +432,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     n0 = (rem - tm * tiles_n) * TN;
   };
 
-  if (warp == 4) {
+  if (warp == kTmaWarp) {
     // ---------------------------------------------------------- TMA producer (both CTAs)
     if (lane == 0) {
       uint32_t it = 0;
@@ -442,7 +453,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer (leader only)
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = ptx::make_idesc_f16(__is_same(T, __nv_bfloat16) ? 1 : 0, 2 * TM, TN, 0, 0);
@@ -477,8 +488,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     }
   } else {
     // -------------------------------------------------------------- epilogue (both CTAs, own lanes)
-    unsigned char* staging = smem + kPairStagingOffset + warp * 2 * kStageBufBytes;
-    uint32_t groups = 0;
+    unsigned char* staging = smem + kPairStagingOffset + warp * kStageBufBytes;
+    const int quarter = warp & 3, col_begin = (warp >> 2) * (TN / 2);
     bool ready = true;
     int lt = 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++lt) {
@@ -487,9 +498,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       const int acc = lt & 1;
       if (ready) ready = ptx::mbar_wait(&tmem_full_bar[acc], (uint32_t)(lt >> 1) & 1u, abort_flag, g.status, 13);
       ptx::tc_fence_after();
-      drain_accumulator<T>(g, tmap_out.m, tiled != 0, staging, groups,
-                           tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * TN),
-                           m0 + (int)rank * TM + warp * 32, n0, z, ready, lane);
+      drain_accumulator<T>(g, tmap_out.m, tiled != 0, staging,
+                           tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * TN),
+                           m0 + (int)rank * TM + quarter * 32, n0, col_begin, z, ready, lane);
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&tmem_empty_bar[acc]), 0));
@@ -503,7 +514,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
   __syncthreads();
   ptx::cluster_sync_all();
   ptx::tc_fence_after();
-  if (warp == 5) ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+  if (warp == kMmaWarp) ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
 }
 
 // Tensor maps of the outputs for the tiled-store epilogue: boxes of 32 rows x 64 columns, 128-byte swizzle.

@@ -17,7 +17,9 @@ Outside ``attention.self`` the dense projections, the activation and the
 layer-0 convolution stay the caller's PyTorch modules; the tail of the two
 output blocks of a layer, ``LayerNorm(dense(x) + residual)``, runs the add and
 the norm as one kernel (``dfl_add_layernorm``) when the block has the Hugging
-Face shape (``dense`` / ``LayerNorm`` / ``dropout``).  There is one backend;
+Face shape (``dense`` / ``LayerNorm`` / ``dropout``), and a 16-bit
+``gelu(dense(x))`` intermediate block runs as one GEMM with the bias and the
+GELU in its epilogue (``dfl_dense``).  There is one backend;
 ``backend="triton"`` is accepted as the legacy name of the fused backend and
 ``backend="torch"`` is refused because no CPU/PyTorch attention ships here.
 """
@@ -67,6 +69,44 @@ def _add_layernorm_op(x: torch.Tensor, residual: torch.Tensor, weight: torch.Ten
 @_add_layernorm_op.register_fake
 def _add_layernorm_fake(x, residual, weight, bias, eps):
     return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+
+@torch.library.custom_op("disentangled_flash_b200::dense_gelu", mutates_args=("status",), device_types="cuda")
+def _dense_gelu_op(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                   status: Optional[torch.Tensor]) -> torch.Tensor:
+    """``gelu(x @ weight^T + bias)`` (erf form) with bias and activation in the GEMM epilogue (``dfl_dense``)."""
+
+    return _cabi.dense(x.contiguous(), weight, bias, activation=_cabi.ACT_GELU, status=status)
+
+
+@_dense_gelu_op.register_fake
+def _dense_gelu_fake(x, weight, bias, status):
+    return x.new_empty(*x.shape[:-1], weight.shape[0])
+
+
+def _is_erf_gelu(fn: Any) -> bool:
+    """``torch.nn.functional.gelu`` in its erf form, as a function, an ``nn.GELU`` or a wrapper module around it."""
+
+    if fn is F.gelu:
+        return True
+    if isinstance(fn, nn.GELU):
+        return fn.approximate == "none"
+    return isinstance(fn, nn.Module) and getattr(fn, "act", None) is F.gelu   # Transformers' GELUActivation
+
+
+def _intermediate_is_fusable(block: nn.Module) -> bool:
+    """Whether ``block`` is ``gelu(dense(x))`` in the Hugging Face shape (``_reference.py:461-471``) in a 16-bit type
+    on a CUDA device, with row lengths the tensor-core GEMM takes."""
+
+    dense = getattr(block, "dense", None)
+    if not isinstance(dense, nn.Linear) or not _is_erf_gelu(getattr(block, "intermediate_act_fn", None)):
+        return False
+    if not {name for name, _ in block.named_children()} <= {"dense", "intermediate_act_fn"}:
+        return False
+    weight = dense.weight
+    return (weight.is_cuda and weight.dtype in (torch.float16, torch.bfloat16)
+            and weight.shape[0] % 8 == 0 and weight.shape[1] % 8 == 0
+            and (dense.bias is None or dense.bias.dtype == weight.dtype))
 
 
 _OUTPUT_BLOCK_CHILDREN = frozenset(("dense", "LayerNorm", "dropout"))
@@ -206,6 +246,7 @@ class DebertaV2InferenceEncoder(nn.Module):
 
         self._buckets = _BucketTable()
         self._fused_output_blocks: list[tuple[bool, bool]] = [(False, False)] * len(self.layer)
+        self._fused_intermediates: list[bool] = [False] * len(self.layer)
         self._status_word: torch.Tensor | None = None
         self.register_load_state_dict_post_hook(_drop_plans_after_load)
 
@@ -289,6 +330,8 @@ class DebertaV2InferenceEncoder(nn.Module):
             (_output_block_is_fusable(layer.attention.output), _output_block_is_fusable(layer.output))
             for layer in self.layer
         ] if device.type == "cuda" else [(False, False)] * len(self.layer)
+        self._fused_intermediates = [device.type == "cuda" and _intermediate_is_fusable(layer.intermediate)
+                                     for layer in self.layer]
         return self
 
     def activate_shape(self, sequence_length: int) -> "DebertaV2InferenceEncoder":
@@ -343,7 +386,12 @@ class DebertaV2InferenceEncoder(nn.Module):
             context, _ = layer.attention.self.forward_prepared(state, keep, plans[depth])
             fuse_attention_output, fuse_output = self._fused_output_blocks[depth]
             mixed = _output_block(layer.attention.output, fuse_attention_output, context, state)
-            state = _output_block(layer.output, fuse_output, layer.intermediate(mixed), mixed)
+            if self._fused_intermediates[depth] and mixed.dtype == layer.intermediate.dense.weight.dtype:
+                dense = layer.intermediate.dense
+                inner = _dense_gelu_op(mixed, dense.weight, dense.bias, self._status_word)
+            else:
+                inner = layer.intermediate(mixed)
+            state = _output_block(layer.output, fuse_output, inner, mixed)
             if depth == 0 and self.conv is not None:
                 # the convolution branch sees the encoder input and the padding mask as the caller gave it
                 state = self.conv(hidden_states, state, attention_mask)

@@ -256,6 +256,29 @@ DFL_API int dfl_attention_rel_supported(const DflAttnRelParams* p);
 DFL_API int dfl_attention_rel_fwd(const DflAttnRelParams* p, void* stream);
 
 /*
+ * Dense layer with the bias and the activation in the GEMM epilogue:
+ *     out[M, N] = act(x[M, K] * w[N, K]^T + bias[N])
+ * Replaces DebertaV2Intermediate.forward (_reference.py:461-471: nn.Linear followed by ACT2FN["gelu"], which PyTorch
+ * runs as a GEMM and an elementwise kernel that reads and writes the [M, N] intermediate once more).  All tensors
+ * row-major, K and N multiples of 8 elements (16-byte rows).  DFL_ACT_GELU is the erf form, 0.5 v (1 + erf(v/sqrt 2)):
+ * the F32 kernels use erff, the F16/BF16 kernels a rational approximation of erf with absolute error < 1.5e-7.
+ */
+#define DFL_ACT_NONE 0
+#define DFL_ACT_GELU 1
+typedef struct DflDenseParams {
+  const void* x;        /* [M, K] */
+  const void* w;        /* [N, K] (nn.Linear weight layout) */
+  const void* bias;     /* [N] or NULL */
+  void*       out;      /* [M, N] */
+  int32_t M, N, K;
+  int32_t activation;   /* DFL_ACT_* */
+  int32_t dtype;        /* DFL_F16 / DFL_BF16 / DFL_F32 */
+  int32_t algo;         /* DFL_ALGO_* */
+  int32_t* status;      /* optional device int32, see dfl_check_status() */
+} DflDenseParams;
+DFL_API int dfl_dense(const DflDenseParams* p, void* stream);
+
+/*
  * Residual add + LayerNorm in one pass (the tail of a layer's two output blocks):
  *     out[r, :] = LayerNorm(x[r, :] + residual[r, :]) * gamma + beta
  * with the sum, the mean and the (biased) variance in fp32 and the result rounded to `dtype`.  Replaces, in the
