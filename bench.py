@@ -684,12 +684,16 @@ def run_attention_sweep(args, ctx: GpuContext) -> None:
 
 # ----------------------------------------------------------------------------- v2-xlarge
 def run_v2_xlarge(args, ctx: GpuContext) -> None:
+    import disentangled_flash_b200 as df
+
     device = ctx.device
     geometry, batch, lengths = "v2-xlarge", 8, (64, 128, 256, 512)
     hidden_size = GEOMETRY[geometry]["hidden"]
     rows = []
     for dtype_name, dtype in (("bf16", torch.bfloat16), ("fp32", torch.float32)):
         _, encoder = build_gpu_encoder(geometry, args.layers, dtype, device, lengths)
+        # one CUDA graph per bucket: at this batch size the eager forward is bound by the host's launch rate
+        graphs = df.capture_deberta_buckets(encoder, batch) if dtype != torch.float32 else {}
         for length in lengths:
             gen = torch.Generator().manual_seed(length)
             inputs = []
@@ -699,29 +703,34 @@ def run_v2_xlarge(args, ctx: GpuContext) -> None:
                 inputs.append((hidden.to(device), (torch.arange(length)[None, :] < valid[:, None]).to(device)))
             encoder.activate_shape(length)
             steps = args.steps
+            modes = [("eager", lambda h, m: encoder(h, m, output_hidden_states=False))]
+            if length in graphs:
+                modes.append(("cuda-graph", graphs[length]))
+            for mode, call in modes:
+                def body():
+                    for i in range(steps):
+                        call(*inputs[i % len(inputs)])
 
-            def body():
-                for i in range(steps):
-                    encoder(*inputs[i % len(inputs)], output_hidden_states=False)
-
-            with torch.inference_mode():
-                for i in range(max(3, args.warmup)):
-                    encoder(*inputs[i % len(inputs)], output_hidden_states=False)
-                ms = timed_region(ctx, body)
-            rows.append({"dtype": dtype_name, "seq_len": length, "batch": batch, "ms_per_step": ms / steps,
-                         "sequences_per_s": batch * steps / (ms / 1e3)})
+                with torch.inference_mode():
+                    for i in range(max(3, args.warmup)):
+                        call(*inputs[i % len(inputs)])
+                    ms = timed_region(ctx, body)
+                rows.append({"dtype": dtype_name, "mode": mode, "seq_len": length, "batch": batch,
+                             "ms_per_step": ms / steps, "sequences_per_s": batch * steps / (ms / 1e3)})
         encoder.check_device_status()
-        del encoder
+        del encoder, graphs
         torch.cuda.empty_cache()
     if ctx.rank == 0:
-        head = next(r for r in rows if (r["dtype"], r["seq_len"]) == ("bf16", 512))
+        head = next(r for r in rows if (r["dtype"], r["mode"], r["seq_len"]) == ("bf16", "cuda-graph", 512))
         emit(json.dumps({
             "metric": "encoder_sequences_per_second", "value": head["sequences_per_s"], "unit": "sequences/s", "n_gpus": 1,
             "steps": args.steps, "higher_is_better": True, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "deberta-v2-xlarge-encoder", **GEOMETRY[geometry], "layers": args.layers or GEOMETRY[geometry]["layers"],
                        "batch": batch, "buckets": list(lengths), "valid_lengths": "uniform[L/2, L]",
-                       "note": "one encoder, four prepared buckets switched with activate_shape(); fp32 = strict IEEE kernels",
-                       "headline_row": "bf16 L=512"},
+                       "note": "one encoder, four prepared buckets; eager = activate_shape() + forward, cuda-graph = "
+                               "capture_deberta_buckets() replay (inputs copied into the graph's buffers inside the "
+                               "timed region); fp32 = strict IEEE kernels, eager only",
+                       "headline_row": "bf16 cuda-graph L=512"},
             "rows": rows}))
 
 

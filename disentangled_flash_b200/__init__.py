@@ -10,6 +10,7 @@ from .attention import B200PreparedPositionPlan, DisentangledFlashAttention
 from .config import DebertaAttentionConfig
 from .encoder import (
     DebertaV2InferenceEncoder,
+    capture_deberta_buckets,
     compile_deberta_buckets,
     enable_deberta_inference,
     enable_deberta_v2_inference,
@@ -26,6 +27,7 @@ __all__ = [
     "DisentangledFlashAttention",
     "SharedPositionIndexPlan",
     "SharedPositionPlanCache",
+    "capture_deberta_buckets",
     "compile_deberta_buckets",
     "enable_deberta_inference",
     "enable_deberta_v2_inference",

@@ -500,11 +500,80 @@ def compile_deberta_buckets(
     return programs
 
 
+class CapturedBucket:
+    """One prepared bucket at one batch size as a CUDA graph: a whole encoder forward is one graph launch.
+
+    Calling it copies ``hidden_states`` and ``attention_mask`` into the graph's input buffers, replays the graph and
+    returns the graph's output buffer - the same tensor on every call, overwritten by the next one (clone it to
+    keep it).  Everything is enqueued on the current stream; nothing synchronises with the host.
+    """
+
+    def __init__(self, graph: "torch.cuda.CUDAGraph", hidden: torch.Tensor, mask: torch.Tensor, out: torch.Tensor):
+        self.graph, self.hidden_states, self.attention_mask, self.last_hidden_state = graph, hidden, mask, out
+
+    def __call__(self, hidden_states: torch.Tensor, attention_mask: torch.Tensor) -> torch.Tensor:
+        if hidden_states.shape != self.hidden_states.shape or attention_mask.shape != self.attention_mask.shape:
+            raise ValueError(
+                f"captured for hidden_states {tuple(self.hidden_states.shape)} and attention_mask "
+                f"{tuple(self.attention_mask.shape)}, got {tuple(hidden_states.shape)} and {tuple(attention_mask.shape)}"
+            )
+        self.hidden_states.copy_(hidden_states, non_blocking=True)
+        self.attention_mask.copy_(attention_mask, non_blocking=True)
+        self.graph.replay()
+        return self.last_hidden_state
+
+
+def capture_deberta_buckets(
+    encoder: DebertaV2InferenceEncoder,
+    batch_size: int,
+    sequence_lengths: Iterable[int] | None = None,
+    *,
+    mask_dtype: torch.dtype = torch.bool,
+    warmup: int = 2,
+) -> dict[int, CapturedBucket]:
+    """One CUDA graph per prepared bucket at a fixed batch size.
+
+    A forward of a small batch is bound by the rate at which the host can launch kernels (some twenty per layer);
+    a captured bucket is launched once.  The reference reaches for ``torch.compile`` here
+    (``compile_deberta_buckets``, ``deberta.py:349-427``); this is the same idea with a stream capture of the
+    prepared forward instead of a tracing compiler.  Each bucket is run ``warmup`` times on a side stream before it is
+    captured, so that every one-time kernel configuration and lazy module load happens outside the capture.
+    """
+
+    if batch_size < 1:
+        raise ValueError("batch_size must be positive")
+    table = encoder._buckets
+    lengths = tuple(sorted(table.by_length)) if sequence_lengths is None else table.require(sequence_lengths)
+    anchor = encoder._attention_modules()[0].query_proj.weight
+    if anchor.device.type != "cuda":
+        raise RuntimeError("capture_deberta_buckets needs the encoder on a CUDA device")
+    hidden_size = anchor.shape[1]
+    captured: dict[int, CapturedBucket] = {}
+    with torch.cuda.device(anchor.device), torch.inference_mode():
+        for length in lengths:
+            plans = table.by_length[length]
+            hidden = torch.zeros(batch_size, length, hidden_size, dtype=anchor.dtype, device=anchor.device)
+            mask = torch.ones(batch_size, length, dtype=mask_dtype, device=anchor.device)
+            side = torch.cuda.Stream(anchor.device)
+            side.wait_stream(torch.cuda.current_stream(anchor.device))
+            with torch.cuda.stream(side):
+                for _ in range(max(1, warmup)):
+                    encoder.forward_prepared(hidden, mask, plans, output_hidden_states=False)
+            torch.cuda.current_stream(anchor.device).wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = encoder.forward_prepared(hidden, mask, plans, output_hidden_states=False).last_hidden_state
+            captured[length] = CapturedBucket(graph, hidden, mask, out)
+    return captured
+
+
 enable_deberta_v2_inference = enable_deberta_inference
 
 __all__ = [
     "BaseModelOutput",
+    "CapturedBucket",
     "DebertaV2InferenceEncoder",
+    "capture_deberta_buckets",
     "compile_deberta_buckets",
     "enable_deberta_inference",
     "enable_deberta_v2_inference",

@@ -115,3 +115,35 @@ def test_compile_deberta_buckets_traces_through_the_custom_op():
         df.compile_deberta_buckets(model.encoder, [32])
     with pytest.raises(ValueError, match="missing compilation example"):
         df.compile_deberta_buckets(model.encoder, [64], examples={})
+
+
+def test_captured_buckets_replay_the_eager_forward_bitwise():
+    """``capture_deberta_buckets``: one CUDA graph per bucket at a fixed batch size; replays equal the eager forward."""
+
+    import hf_modules
+    import disentangled_flash_b200 as df
+
+    cfg = df.DebertaAttentionConfig(hidden_size=128, num_attention_heads=2, attention_head_size=64,
+                                    num_hidden_layers=2, intermediate_size=256, max_position_embeddings=512,
+                                    position_buckets=256, norm_rel_ebd="layer_norm", conv_kernel_size=3)
+    backbone = hf_modules.Backbone(cfg, vocab_size=8).eval()
+    hf_modules.initialize_parameters(backbone, 9)
+    backbone = backbone.to(dev, torch.float16)
+    df.optimize_deberta(backbone, sequence_lengths=[64, 160])
+    encoder = backbone.encoder
+    graphs = df.capture_deberta_buckets(encoder, batch_size=3)
+    assert sorted(graphs) == [64, 160]
+    gen = torch.Generator().manual_seed(2)
+    for round_ in range(2):
+        for length in (160, 64):
+            hidden = torch.randn(3, length, 128, generator=gen).mul_(0.5).to(torch.float16).to(dev)
+            valid = torch.randint(1, length + 1, (3,), generator=gen)
+            mask = (torch.arange(length)[None, :] < valid[:, None]).to(dev)
+            got = graphs[length](hidden, mask).clone()
+            encoder.activate_shape(length)
+            with torch.inference_mode():
+                want = encoder(hidden, mask, output_hidden_states=False).last_hidden_state
+            assert torch.equal(got, want), f"bucket {length}, round {round_}"
+    encoder.check_device_status()
+    with pytest.raises(ValueError, match="captured for"):
+        graphs[64](torch.zeros(2, 64, 128, dtype=torch.float16, device=dev), torch.ones(2, 64, dtype=torch.bool, device=dev))
