@@ -549,11 +549,13 @@ def capture_deberta_buckets(
         raise RuntimeError("capture_deberta_buckets needs the encoder on a CUDA device")
     hidden_size = anchor.shape[1]
     captured: dict[int, CapturedBucket] = {}
+    # the input buffers are ordinary tensors (callers copy into them outside inference mode)
+    buffers = {length: (torch.zeros(batch_size, length, hidden_size, dtype=anchor.dtype, device=anchor.device),
+                        torch.ones(batch_size, length, dtype=mask_dtype, device=anchor.device)) for length in lengths}
     with torch.cuda.device(anchor.device), torch.inference_mode():
         for length in lengths:
             plans = table.by_length[length]
-            hidden = torch.zeros(batch_size, length, hidden_size, dtype=anchor.dtype, device=anchor.device)
-            mask = torch.ones(batch_size, length, dtype=mask_dtype, device=anchor.device)
+            hidden, mask = buffers[length]
             side = torch.cuda.Stream(anchor.device)
             side.wait_stream(torch.cuda.current_stream(anchor.device))
             with torch.cuda.stream(side):
