@@ -189,7 +189,7 @@ class LaunchObserver:
 
     KERNELS = {"linear_heads": "dfl_qkv_proj", "pos_scores": "dfl_pos_scores", "attention_fwd": "dfl_attention_fwd",
                "attention_rel_fwd": "dfl_attention_rel_fwd", "attention_fwd_static": "dfl_attention_fwd_static",
-               "add_layernorm": "dfl_add_layernorm", "dense": "dfl_dense"}
+               "add_layernorm": "dfl_add_layernorm", "dense": "dfl_dense", "conv1d": "dfl_conv1d"}
     TIMED = ("dfl_attention_fwd", "dfl_attention_rel_fwd")
 
     def __init__(self):

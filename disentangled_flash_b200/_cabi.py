@@ -41,6 +41,8 @@ EXPORTED_SYMBOLS = (
     "dfl_gather_slots",
     "dfl_add_layernorm",
     "dfl_dense",
+    "dfl_conv1d",
+    "dfl_conv1d_supported",
     "dfl_add_layernorm_supported",
     "dfl_pos_scores",
     "dfl_attention_fwd",
@@ -104,12 +106,19 @@ class DflDenseParams(Structure):
                 ("algo", c_int32), ("status", c_void_p)]
 
 
-ACT_NONE, ACT_GELU = 0, 1
+ACT_NONE, ACT_GELU, ACT_TANH = 0, 1, 2
+
+
+class DflConv1dParams(Structure):
+    _fields_ = [("x", c_void_p), ("w", c_void_p), ("bias", c_void_p), ("row_mask", c_void_p), ("out", c_void_p),
+                ("batch", c_int32), ("seq_len", c_int32), ("c_in", c_int32), ("c_out", c_int32), ("taps", c_int32),
+                ("mask_elem_size", c_int32), ("activation", c_int32), ("dtype", c_int32), ("status", c_void_p)]
 
 
 class DflAddLayerNormParams(Structure):
     _fields_ = [("x", c_void_p), ("residual", c_void_p), ("gamma", c_void_p), ("beta", c_void_p), ("out", c_void_p),
-                ("rows", ctypes.c_int64), ("hidden", c_int), ("eps", ctypes.c_float), ("dtype", c_int)]
+                ("rows", ctypes.c_int64), ("hidden", c_int), ("eps", ctypes.c_float), ("dtype", c_int),
+                ("row_mask", c_void_p), ("mask_elem_size", c_int)]
 
 
 class DflError(RuntimeError):
@@ -146,6 +155,10 @@ def load_library() -> ctypes.CDLL:
     lib.dfl_build_position_lut.argtypes = [c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.dfl_qkv_proj.restype = c_int
     lib.dfl_qkv_proj.argtypes = [POINTER(DflLinearParams), c_void_p]
+    lib.dfl_conv1d_supported.restype = c_int
+    lib.dfl_conv1d_supported.argtypes = [POINTER(DflConv1dParams)]
+    lib.dfl_conv1d.restype = c_int
+    lib.dfl_conv1d.argtypes = [POINTER(DflConv1dParams), c_void_p]
     lib.dfl_dense.restype = c_int
     lib.dfl_dense.argtypes = [POINTER(DflDenseParams), c_void_p]
     lib.dfl_add_layernorm_supported.restype = c_int
@@ -323,9 +336,52 @@ def add_layernorm_supported(dtype: torch.dtype, hidden: int) -> bool:
     return bool(load_library().dfl_add_layernorm_supported(dtype_code(dtype), int(hidden)))
 
 
+def _conv1d_params(x, weight, bias, row_mask, out, activation, status) -> DflConv1dParams:
+    p = DflConv1dParams()
+    p.x, p.w, p.bias, p.row_mask, p.out = _ptr(x), _ptr(weight), _ptr(bias), _ptr(row_mask), _ptr(out)
+    p.batch, p.seq_len, p.c_in = x.shape
+    p.taps, p.c_out = weight.shape[0], weight.shape[1]
+    p.mask_elem_size = row_mask.element_size() if row_mask is not None else 1
+    p.activation, p.dtype, p.status = activation, dtype_code(x.dtype), _ptr(status)
+    return p
+
+
+def conv1d_supported(dtype: torch.dtype, seq_len: int, c_in: int, c_out: int, taps: int, activation: int) -> bool:
+    """Whether ``conv1d`` covers this configuration."""
+
+    if dtype not in (torch.float16, torch.bfloat16):
+        return False
+    p = DflConv1dParams()
+    p.batch, p.seq_len, p.c_in, p.c_out, p.taps = 1, seq_len, c_in, c_out, taps
+    p.activation, p.dtype, p.mask_elem_size = activation, dtype_code(dtype), 1
+    return bool(load_library().dfl_conv1d_supported(ctypes.byref(p)))
+
+
+def conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, row_mask: torch.Tensor | None, *,
+           activation: int = ACT_NONE, status: torch.Tensor | None = None) -> torch.Tensor:
+    """``act(keep * (conv1d(x) + bias))`` over the sequence: x [B, L, C_in], weight [taps, C_out, C_in] -> [B, L, C_out]."""
+
+    lib = load_library()
+    for name, t in (("x", x), ("weight", weight), ("bias", bias), ("row_mask", row_mask)):
+        if t is not None:
+            _require_cuda_contiguous(name, t)
+    if weight.dtype != x.dtype or (bias is not None and bias.dtype != x.dtype):
+        raise TypeError("weight and bias must have the dtype of x")
+    if x.dim() != 3 or weight.dim() != 3 or weight.shape[2] != x.shape[2]:
+        raise ValueError("x must be [B, L, C_in] and weight [taps, C_out, C_in]")
+    if row_mask is not None and tuple(row_mask.shape) != tuple(x.shape[:2]):
+        raise ValueError("row_mask must be [B, L]")
+    out = torch.empty(x.shape[0], x.shape[1], weight.shape[1], dtype=x.dtype, device=x.device)
+    p = _conv1d_params(x, weight, bias, row_mask, out, activation, status)
+    with torch.cuda.device(x.device):
+        _check(lib.dfl_conv1d(ctypes.byref(p), _stream(x.device)), "dfl_conv1d")
+    return out
+
+
 def add_layernorm(x: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor | None,
-                  eps: float, out: torch.Tensor | None = None) -> torch.Tensor:
-    """``LayerNorm(x + residual) * weight + bias`` over the last dimension, sum and statistics in fp32."""
+                  eps: float, out: torch.Tensor | None = None, row_mask: torch.Tensor | None = None) -> torch.Tensor:
+    """``LayerNorm(x + residual) * weight + bias`` over the last dimension, sum and statistics in fp32; rows whose
+    ``row_mask`` element is zero are written as zeros."""
 
     lib = load_library()
     hidden = x.shape[-1]
@@ -344,6 +400,11 @@ def add_layernorm(x: torch.Tensor, residual: torch.Tensor | None, weight: torch.
     p = DflAddLayerNormParams()
     p.x, p.residual, p.gamma, p.beta, p.out = _ptr(x), _ptr(residual), _ptr(weight), _ptr(bias), _ptr(out)
     p.rows, p.hidden, p.eps, p.dtype = x.numel() // hidden, hidden, float(eps), dtype_code(x.dtype)
+    if row_mask is not None:
+        _require_cuda_contiguous("row_mask", row_mask)
+        if row_mask.numel() != p.rows:
+            raise ValueError("row_mask must have one element per row of x")
+        p.row_mask, p.mask_elem_size = _ptr(row_mask), row_mask.element_size()
     with torch.cuda.device(x.device):
         _check(lib.dfl_add_layernorm(ctypes.byref(p), _stream(x.device)), "dfl_add_layernorm")
     return out

@@ -95,7 +95,8 @@ __device__ __forceinline__ uint4 ld_stream(const uint4* p) {   // read once: do 
 template <typename T, int VEC>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 add_layernorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ residual, const uint4* __restrict__ gamma,
-                     const uint4* __restrict__ beta, uint4* __restrict__ out, long long rows, int hidden, float eps) {
+                     const uint4* __restrict__ beta, uint4* __restrict__ out, long long rows, int hidden, float eps,
+                     const void* __restrict__ row_mask, int mask_elem) {
   constexpr int E = Vec16<T>::kElems;
   const int lane = threadIdx.x & 31;
   const int vecs_per_row = hidden / E;
@@ -144,7 +145,9 @@ add_layernorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ resi
         }
       }
     }
-    const float rstd = rsqrtf(warp_sum(sq) * inv_n + eps);
+    // rows the mask drops are written as zeros (the convolution branch multiplies its output by the padding mask)
+    const float keep = row_mask && !mask_keep(row_mask, mask_elem, row) ? 0.0f : 1.0f;
+    const float rstd = rsqrtf(warp_sum(sq) * inv_n + eps) * keep;
     uint4* orow = out + row * vecs_per_row;
 #pragma unroll
     for (int j = 0; j < VEC; ++j) {
@@ -154,7 +157,7 @@ add_layernorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ resi
         unpack<T>(__ldg(gamma + c), g);
         if (beta) unpack<T>(__ldg(beta + c), b);
 #pragma unroll
-        for (int e = 0; e < E; ++e) y[e] = fmaf((v[j * E + e] - mean) * rstd, g[e], beta ? b[e] : 0.f);
+        for (int e = 0; e < E; ++e) y[e] = fmaf((v[j * E + e] - mean) * rstd, g[e], beta ? b[e] * keep : 0.f);
         orow[c] = pack<T>(y);
       }
     }
@@ -163,22 +166,23 @@ add_layernorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ resi
 
 template <typename T, int VEC>
 void launch_one(const void* x, const void* residual, const void* gamma, const void* beta, void* out, long long rows,
-                int hidden, float eps, int sm_count, cudaStream_t stream) {
+                int hidden, float eps, const void* row_mask, int mask_elem, int sm_count, cudaStream_t stream) {
   const long long wanted = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
   const long long cap = (long long)sm_count * 8;   // 8 CTAs of 8 warps per SM: one wave, grid-stride beyond it
   const int blocks = (int)(wanted < cap ? wanted : cap);
   add_layernorm_kernel<T, VEC><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
-      (const uint4*)x, (const uint4*)residual, (const uint4*)gamma, (const uint4*)beta, (uint4*)out, rows, hidden, eps);
+      (const uint4*)x, (const uint4*)residual, (const uint4*)gamma, (const uint4*)beta, (uint4*)out, rows, hidden, eps,
+      row_mask, mask_elem);
 }
 
 template <typename T>
 int launch_typed(const void* x, const void* residual, const void* gamma, const void* beta, void* out, long long rows,
-                 int hidden, float eps, int sm_count, cudaStream_t stream) {
+                 int hidden, float eps, const void* row_mask, int mask_elem, int sm_count, cudaStream_t stream) {
   constexpr int E = Vec16<T>::kElems;
   const int vec = (hidden / E + 31) / 32;
 #define DFL_LN_CASE(V)                                                                              \
   if (vec <= V) {                                                                                   \
-    launch_one<T, V>(x, residual, gamma, beta, out, rows, hidden, eps, sm_count, stream);          \
+    launch_one<T, V>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, sm_count, stream); \
     return check_launch("add_layernorm_kernel");                                                    \
   }
   DFL_LN_CASE(1) DFL_LN_CASE(2) DFL_LN_CASE(3) DFL_LN_CASE(4) DFL_LN_CASE(6) DFL_LN_CASE(8) DFL_LN_CASE(12)
@@ -192,14 +196,15 @@ int launch_typed(const void* x, const void* residual, const void* gamma, const v
 int add_layernorm_max_hidden(size_t elem_size) { return 16 * 32 * (int)(16 / elem_size); }
 
 int launch_add_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* out,
-                         long long rows, int hidden, float eps, int dtype, cudaStream_t stream) {
+                         long long rows, int hidden, float eps, int dtype, const void* row_mask, int mask_elem,
+                         cudaStream_t stream) {
   static KernelDeviceConfig config;   // only the SM count of the current device is needed (no shared memory)
   int sm_count = 0;
   if (int rc = configure_kernel(config, add_layernorm_kernel<float, 1>, 0, &sm_count, "add_layernorm_kernel")) return rc;
   switch (dtype) {
-    case DFL_F16: return launch_typed<__half>(x, residual, gamma, beta, out, rows, hidden, eps, sm_count, stream);
-    case DFL_BF16: return launch_typed<__nv_bfloat16>(x, residual, gamma, beta, out, rows, hidden, eps, sm_count, stream);
-    default: return launch_typed<float>(x, residual, gamma, beta, out, rows, hidden, eps, sm_count, stream);
+    case DFL_F16: return launch_typed<__half>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, sm_count, stream);
+    case DFL_BF16: return launch_typed<__nv_bfloat16>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, sm_count, stream);
+    default: return launch_typed<float>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, sm_count, stream);
   }
 }
 

@@ -180,7 +180,7 @@ int dfl_dense(const DflDenseParams* p, void* stream) {
   if (!valid_dtype(p->dtype)) return fail(DFL_ERR_BAD_ARG, "unknown dtype %d", p->dtype);
   if (p->M < 0 || p->N < 1 || p->K < 1) return fail(DFL_ERR_BAD_ARG, "non-positive size");
   if (p->activation != DFL_ACT_NONE && p->activation != DFL_ACT_GELU)
-    return fail(DFL_ERR_BAD_ARG, "unknown activation %d", p->activation);
+    return fail(DFL_ERR_BAD_ARG, "dfl_dense takes DFL_ACT_NONE or DFL_ACT_GELU, got %d", p->activation);
   if (p->M == 0) return DFL_OK;
   if (!p->x || !p->w || !p->out) return fail(DFL_ERR_BAD_ARG, "null pointer");
   if ((p->N % 8) || (p->K % 8)) return fail(DFL_ERR_ALIGNMENT, "N and K must be multiples of 8 elements");
@@ -197,6 +197,43 @@ int dfl_dense(const DflDenseParams* p, void* stream) {
   g.activation = p->activation;
   return use_tensor_cores(p->dtype, p->algo) ? launch_gemm_tc(g, (cudaStream_t)stream)
                                              : launch_gemm_simt(g, (cudaStream_t)stream);
+}
+
+int dfl_conv1d_supported(const DflConv1dParams* p) {
+  if (!p || (p->dtype != DFL_F16 && p->dtype != DFL_BF16)) return 0;
+  if (p->taps < 1 || p->taps > 9 || !(p->taps & 1)) return 0;
+  if (p->seq_len < 256 || p->c_in < 64 || (p->c_in % 8) || (p->c_out % 8) || p->c_out < 8) return 0;
+  return p->activation == DFL_ACT_NONE || p->activation == DFL_ACT_GELU || p->activation == DFL_ACT_TANH;
+}
+
+int dfl_conv1d(const DflConv1dParams* p, void* stream) {
+  if (!p) return fail(DFL_ERR_BAD_ARG, "null params");
+  if (!valid_dtype(p->dtype)) return fail(DFL_ERR_BAD_ARG, "unknown dtype %d", p->dtype);
+  if (p->batch < 1 || p->seq_len < 1 || p->c_in < 1 || p->c_out < 1) return fail(DFL_ERR_BAD_ARG, "non-positive size");
+  if (!dfl_conv1d_supported(p))
+    return fail(DFL_ERR_UNSUPPORTED,
+                "conv1d covers F16/BF16, odd taps <= 9, seq_len >= 256, c_in >= 64, channels in multiples of 8");
+  if (!p->x || !p->w || !p->out) return fail(DFL_ERR_BAD_ARG, "null pointer");
+  if (p->row_mask && p->mask_elem_size != 1 && p->mask_elem_size != 4 && p->mask_elem_size != 8)
+    return fail(DFL_ERR_BAD_ARG, "mask_elem_size must be 1, 4 or 8");
+  if (!aligned16(p->x) || !aligned16(p->w) || !aligned16(p->out) || !aligned16(p->bias))
+    return fail(DFL_ERR_ALIGNMENT, "pointers must be 16-byte aligned");
+  if ((long long)p->batch > 65535) return fail(DFL_ERR_TOO_LARGE, "batch beyond 65535");
+  GemmDesc g{};
+  g.x = p->x; g.w = p->w; g.bias = p->bias; g.out[0] = p->out;
+  g.M = p->seq_len; g.N = p->c_out; g.K = p->c_in;
+  g.batch = p->batch;
+  g.stride_x = (long long)p->seq_len * p->c_in;
+  g.stride_w = 0; g.w_mod = 1;
+  g.stride_c = (long long)p->seq_len * p->c_out;
+  g.ldc = p->c_out;
+  g.head_split = 0; g.heads = 1; g.head_dim = p->c_out; g.rows_per_seq = p->seq_len;
+  g.dtype = p->dtype;
+  g.status = p->status;
+  g.activation = p->activation;
+  g.taps = p->taps;
+  g.row_mask = p->row_mask; g.row_mask_elem = p->mask_elem_size;
+  return launch_gemm_tc(g, (cudaStream_t)stream);
 }
 
 int dfl_add_layernorm_supported(int dtype, int hidden) {
@@ -217,8 +254,10 @@ int dfl_add_layernorm(const DflAddLayerNormParams* p, void* stream) {
   if (!p->x || !p->gamma || !p->out) return fail(DFL_ERR_BAD_ARG, "null pointer");
   if (!aligned16(p->x) || !aligned16(p->residual) || !aligned16(p->gamma) || !aligned16(p->beta) || !aligned16(p->out))
     return fail(DFL_ERR_ALIGNMENT, "pointers must be 16-byte aligned");
+  if (p->row_mask && p->mask_elem_size != 1 && p->mask_elem_size != 4 && p->mask_elem_size != 8)
+    return fail(DFL_ERR_BAD_ARG, "mask_elem_size must be 1, 4 or 8");
   return launch_add_layernorm(p->x, p->residual, p->gamma, p->beta, p->out, p->rows, p->hidden, p->eps, p->dtype,
-                              (cudaStream_t)stream);
+                              p->row_mask, p->mask_elem_size, (cudaStream_t)stream);
 }
 
 int dfl_attention_rel_supported(const DflAttnRelParams* p) {

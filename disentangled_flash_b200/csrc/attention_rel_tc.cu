@@ -752,27 +752,29 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       const ItemSlot* sl = &slots[slot];
       const int n = sl->t_end - sl->t_begin;
       if (sl->any_kept != 0) {
-        // jobs of the item in production order: block 0 | P2C of tile 0 | block 1 | per further tile u: first half,
-        // block u + 1, second half
+        // Jobs of the item in production order: block 0 | P2C of tile 0 | block 1 | per further tile u: first half,
+        // block u + 1, second half.  One flat loop with one copy of each conversion routine: the converter's code
+        // shares the instruction cache with the softmax warps of its scheduler.
         for (int u = 0; u < n && ok; ++u) {
-          if (u == 0) {
-            if (has_c2p) {
-              ok = convert_block(t_xc, &bars->xc_full, c_xc & 1u, true, 0, tiles_before);
-              ++c_xc;
+#pragma unroll 1
+          for (int jb = 0; jb < 4 && ok; ++jb) {
+            // kind: 0 nothing, 1 C2P block from the XC accumulator, 2 C2P block from the P/O columns, 3 P2C half
+            int kind, arg;
+            if (u == 0) {
+              kind = jb == 0 ? 1 : (jb == 3 ? 2 : 3);
+              arg = jb == 0 ? 0 : (jb == 3 ? 1 : jb - 1);          // ring position / half
+            } else {
+              kind = jb == 0 ? 0 : (jb == 2 ? 1 : 3);
+              arg = jb == 2 ? ((u + 1) & 1) : (jb == 1 ? 0 : 1);   // block u + 1 replaces block u - 1
             }
-            if (ok && has_p2c) ok = convert_half(0) && convert_half(1);
-            if (ok && has_c2p) {
-              ok = convert_block(t_b1, &bars->b1_full, c_b1 & 1u, false, 1, tiles_before);
-              ++c_b1;
+            if (kind == 3) {
+              if (has_p2c) ok = convert_half(arg);
+            } else if (kind != 0 && has_c2p) {
+              const bool from_xc = kind == 1;
+              ok = convert_block(from_xc ? t_xc : t_b1, from_xc ? &bars->xc_full : &bars->b1_full,
+                                 (from_xc ? c_xc : c_b1) & 1u, from_xc, arg, tiles_before + (uint32_t)u);
+              if (from_xc) ++c_xc; else ++c_b1;
             }
-          } else {
-            if (has_p2c) ok = convert_half(0);
-            if (ok && has_c2p) {
-              // block u + 1 replaces block u - 1, last read by tile u - 1
-              ok = convert_block(t_xc, &bars->xc_full, c_xc & 1u, true, (u + 1) & 1, tiles_before + (uint32_t)u);
-              ++c_xc;
-            }
-            if (ok && has_p2c) ok = convert_half(1);
           }
           if (!ok) break;
           __syncwarp();

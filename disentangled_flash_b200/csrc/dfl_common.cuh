@@ -129,7 +129,21 @@ struct GemmDesc {
   int dtype;
   int* status;          // device status word of the call, or null (the tcgen05 GEMM then uses the library's word)
   int activation;       // DFL_ACT_*: applied after the bias (row-major epilogue only)
+  // 1-D convolution as a GEMM over taps (tensor-core pair kernel only): k-step (tap, kb) multiplies rows
+  // m + tap - taps/2 of X_z (rows outside [0, M) read as zero: 'same' padding) with weight matrix W[tap].
+  int taps;             // 0 or 1: plain GEMM
+  const void* row_mask; // [batch, M] or null: output rows whose element is zero are set to 0 before the activation
+  int row_mask_elem;    // element size of row_mask: 1, 4 or 8 bytes
 };
+
+// tanh for the GEMM epilogues of 16-bit outputs: 1 - 2 / (1 + e^(2x)) with approximate exp2 and reciprocal
+// (absolute error ~1e-7; exact limits +-1).
+__device__ __forceinline__ float tanh_fast(float x) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.8853900817779268f));   // 2 log2(e)
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return fmaf(-2.0f, r, 1.0f);
+}
 
 // GELU, 0.5 x (1 + erf(x / sqrt 2)), for the GEMM epilogues.
 // Exact form (strict FP32 kernels): the CUDA library's erff.
@@ -161,7 +175,8 @@ bool attention_rel_supported(const DflAttnRelParams& p);
 int launch_attention_rel(const DflAttnRelParams& p, cudaStream_t stream);
 int add_layernorm_max_hidden(size_t elem_size);
 int launch_add_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* out,
-                         long long rows, int hidden, float eps, int dtype, cudaStream_t stream);
+                         long long rows, int hidden, float eps, int dtype, const void* row_mask, int mask_elem,
+                         cudaStream_t stream);
 int launch_selftest_bounded_wait(int* status, uint32_t limit_us, cudaStream_t stream);
 int launch_expand_rel_tables(const void* pos, const int32_t* lut, void* rel, int heads, int n_active, int seq_len,
                              int head_dim, int dtype, cudaStream_t stream);

@@ -175,6 +175,9 @@ __device__ __forceinline__ void drain_accumulator(const GemmDesc& g, const CUten
     }
     return;
   }
+  // padding mask of this thread's output row (convolution epilogue)
+  bool keep_row = true;
+  if (g.row_mask && m_warp + lane < g.M) keep_row = mask_keep(g.row_mask, g.row_mask_elem, (long long)z * g.M + m_warp + lane);
 #pragma unroll 1
   for (int c0 = col_begin; c0 < col_begin + TN / 2; c0 += kStageCols) {
     const int n = n0 + c0;
@@ -198,9 +201,16 @@ __device__ __forceinline__ void drain_accumulator(const GemmDesc& g, const CUten
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] += Elem<T>::to_f(bh[j]);
       }
+      if (!keep_row) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = 0.0f;
+      }
       if (g.activation == DFL_ACT_GELU) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = gelu_erf_fast(f[j]);
+      } else if (g.activation == DFL_ACT_TANH) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = tanh_fast(f[j]);
       }
       uint4 packed;
       T* ph = reinterpret_cast<T*>(&packed);
@@ -440,7 +450,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         int m0, n0, z;
         tile_coords(tile, m0, n0, z);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        // k-steps: num_kb = taps x (k-blocks per tap); a plain GEMM has one tap with no row shift
+        const int taps = g.taps > 1 ? g.taps : 1;
+        const int kb_per_tap = num_kb / taps;
+        int tap = 0, kb = 0;
+        for (int step = 0; step < num_kb; ++step, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           ok = ptx::mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, g.status, 11);
@@ -448,8 +462,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
           if (rank == 0) ptx::mbar_arrive_expect_tx(&full_bar[s], 2u * (uint32_t)kPairStageBytes);
           const uint32_t leader_full = ptx::map_to_cta(ptx::smem_u32(&full_bar[s]), 0);
           unsigned char* a = smem + s * kPairStageBytes;
-          ptx::tma_load_3d_pair(a, &tmap_x, leader_full, kb * BK, m0 + (int)rank * TM, z);
-          ptx::tma_load_3d_pair(a + kTileA, &tmap_w, leader_full, kb * BK, n0 + (int)rank * (TN / 2), z % g.w_mod);
+          // rows above the first or below the last row of X_z are filled with zeros by the load
+          ptx::tma_load_3d_pair(a, &tmap_x, leader_full, kb * BK, m0 + (int)rank * TM + tap - (taps >> 1), z);
+          ptx::tma_load_3d_pair(a + kTileA, &tmap_w, leader_full, kb * BK, n0 + (int)rank * (TN / 2),
+                                taps > 1 ? tap : z % g.w_mod);
+          if (++kb == kb_per_tap) {
+            kb = 0;
+            ++tap;
+          }
         }
       }
     }
@@ -546,8 +566,10 @@ int launch_pair(const GemmDesc& g, cudaStream_t stream) {
   const size_t es = sizeof(T);
   CUtensorMap tmap_x, tmap_w;
   const uint64_t x_batch_stride = g.batch > 1 ? (uint64_t)g.stride_x * es : (uint64_t)g.M * g.K * es;
-  const int w_batches = g.w_mod > 1 ? g.w_mod : 1;
-  const uint64_t w_batch_stride = w_batches > 1 ? (uint64_t)g.stride_w * es : (uint64_t)g.N * g.K * es;
+  const int taps = g.taps > 1 ? g.taps : 1;
+  const int w_batches = taps > 1 ? taps : (g.w_mod > 1 ? g.w_mod : 1);
+  const uint64_t w_batch_stride = taps > 1 ? (uint64_t)g.N * g.K * es
+                                  : (w_batches > 1 ? (uint64_t)g.stride_w * es : (uint64_t)g.N * g.K * es);
   int rc = encode_tensor_map_3d(&tmap_x, g.x, g.K, g.M, g.batch, (uint64_t)g.K * es, x_batch_stride, BK, TM, BK * 2);
   if (rc != DFL_OK) return rc;
   rc = encode_tensor_map_3d(&tmap_w, g.w, g.K, g.N, w_batches, (uint64_t)g.K * es, w_batch_stride, BK, TN / 2, BK * 2);
@@ -573,7 +595,7 @@ int launch_pair(const GemmDesc& g, cudaStream_t stream) {
   if (num_tiles > 0x7fffffff) return fail(DFL_ERR_TOO_LARGE, "gemm_tc: too many tiles");
   const long long max_pairs = num_sms / 2;
   const int pairs = (int)(num_tiles < max_pairs ? num_tiles : max_pairs);
-  const int num_kb = (g.K + BK - 1) / BK;
+  const int num_kb = taps * ((g.K + BK - 1) / BK);
   kernel<<<2 * pairs, kThreads, kPairSmem, stream>>>(tmap_x, tmap_w, tmap_out, gd, num_kb, tiles_n, tiles_m,
                                                      (int)num_tiles, tiled);
   return check_launch("gemm_tc_pair_kernel");
@@ -625,6 +647,7 @@ int launch_t(const GemmDesc& g, cudaStream_t stream) {
   if (g.bias && !aligned16(g.bias)) return fail(DFL_ERR_ALIGNMENT, "bias not 16-byte aligned");
   // CTA pairs on 256 x 256 tiles when the problem has at least one full pair tile of rows and a 64-wide k-step
   if (g.K >= 64 && g.M >= 2 * TM) return launch_pair<T>(g, stream);
+  if (g.taps > 1 || g.row_mask) return fail(DFL_ERR_UNSUPPORTED, "taps and row masks need the pair kernel (M >= 256, K >= 64)");
   return g.K >= 64 ? launch_bk<T, 64>(g, stream) : launch_bk<T, 32>(g, stream);
 }
 

@@ -19,7 +19,10 @@ output blocks of a layer, ``LayerNorm(dense(x) + residual)``, runs the add and
 the norm as one kernel (``dfl_add_layernorm``) when the block has the Hugging
 Face shape (``dense`` / ``LayerNorm`` / ``dropout``), and a 16-bit
 ``gelu(dense(x))`` intermediate block runs as one GEMM with the bias and the
-GELU in its epilogue (``dfl_dense``).  There is one backend;
+GELU in its epilogue (``dfl_dense``); the layer-0 convolution branch runs as a
+GEMM over the taps (``dfl_conv1d``) plus the masked add-and-norm when it is a
+plain ``nn.Conv1d`` with ``tanh`` or ``gelu`` in a 16-bit type and the bucket has
+at least 256 positions.  There is one backend;
 ``backend="triton"`` is accepted as the legacy name of the fused backend and
 ``backend="torch"`` is refused because no CPU/PyTorch attention ships here.
 """
@@ -82,6 +85,48 @@ def _dense_gelu_op(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
 @_dense_gelu_op.register_fake
 def _dense_gelu_fake(x, weight, bias, status):
     return x.new_empty(*x.shape[:-1], weight.shape[0])
+
+
+@torch.library.custom_op("disentangled_flash_b200::conv_branch", mutates_args=("status",), device_types="cuda")
+def _conv_branch_op(hidden_states: torch.Tensor, residual: torch.Tensor, attention_mask: torch.Tensor,
+                    conv_weight: torch.Tensor, conv_bias: Optional[torch.Tensor], norm_weight: torch.Tensor,
+                    norm_bias: Optional[torch.Tensor], eps: float, activation: int,
+                    status: Optional[torch.Tensor]) -> torch.Tensor:
+    """The layer-0 convolution branch, ``keep * LayerNorm(residual + act(keep * conv1d(hidden_states)))``
+    (``_reference.py:534-568``), as two kernels: ``dfl_conv1d`` (GEMM over the taps with bias, mask and activation in
+    its epilogue) and ``dfl_add_layernorm`` (with the mask)."""
+
+    keep = attention_mask
+    if keep.dtype not in (torch.bool, torch.uint8, torch.int32, torch.int64):
+        keep = keep != 0
+    keep = keep.contiguous()
+    out = _cabi.conv1d(hidden_states.contiguous(), conv_weight, conv_bias, keep, activation=activation, status=status)
+    return _cabi.add_layernorm(out, residual.contiguous(), norm_weight, norm_bias, eps, out=out, row_mask=keep)
+
+
+@_conv_branch_op.register_fake
+def _conv_branch_fake(hidden_states, residual, attention_mask, conv_weight, conv_bias, norm_weight, norm_bias, eps,
+                      activation, status):
+    return torch.empty_like(residual, memory_format=torch.contiguous_format)
+
+
+_CONV_ACTIVATIONS = {"tanh": _cabi.ACT_TANH, "gelu": _cabi.ACT_GELU}
+
+
+def _conv_activation(module: nn.Module) -> int | None:
+    """Activation code of a Hugging Face ``ConvLayer`` if the branch has the shape the fused kernels cover."""
+
+    conv, norm = getattr(module, "conv", None), getattr(module, "LayerNorm", None)
+    if not (isinstance(conv, nn.Conv1d) and isinstance(norm, nn.LayerNorm) and norm.weight is not None):
+        return None
+    if not {name for name, _ in module.named_children()} <= {"conv", "LayerNorm", "dropout"}:
+        return None
+    taps = conv.kernel_size[0]
+    plain = (conv.groups == 1 and conv.stride == (1,) and conv.dilation == (1,) and conv.padding_mode == "zeros"
+             and taps % 2 == 1 and conv.padding == ((taps - 1) // 2,))
+    if not plain or not conv.weight.is_cuda or conv.weight.dtype != norm.weight.dtype:
+        return None
+    return _CONV_ACTIVATIONS.get(getattr(module, "conv_act", None))
 
 
 def _is_erf_gelu(fn: Any) -> bool:
@@ -247,6 +292,9 @@ class DebertaV2InferenceEncoder(nn.Module):
         self._buckets = _BucketTable()
         self._fused_output_blocks: list[tuple[bool, bool]] = [(False, False)] * len(self.layer)
         self._fused_intermediates: list[bool] = [False] * len(self.layer)
+        self._conv_fused: dict[int, bool] = {}       # per bucket length: the fused convolution branch covers it
+        self._conv_weight: torch.Tensor | None = None   # nn.Conv1d weight as [taps, out, in]
+        self._conv_activation_code = 0
         self._status_word: torch.Tensor | None = None
         self.register_load_state_dict_post_hook(_drop_plans_after_load)
 
@@ -287,6 +335,7 @@ class DebertaV2InferenceEncoder(nn.Module):
         ``_apply`` i.e. ``.to()/.half()/...``, and ``load_state_dict``)."""
 
         self._buckets.reset()
+        self._conv_fused, self._conv_weight = {}, None
         self.position_plan_cache.clear()
         for attention in self._attention_modules():
             attention.clear_inference_cache()
@@ -332,6 +381,16 @@ class DebertaV2InferenceEncoder(nn.Module):
         ] if device.type == "cuda" else [(False, False)] * len(self.layer)
         self._fused_intermediates = [device.type == "cuda" and _intermediate_is_fusable(layer.intermediate)
                                      for layer in self.layer]
+        self._conv_fused, self._conv_weight = {}, None
+        activation = _conv_activation(self.conv) if self.conv is not None and device.type == "cuda" else None
+        if activation is not None:
+            weight = self.conv.conv.weight   # [out, in, taps]
+            c_out, c_in, taps = weight.shape
+            self._conv_activation_code = activation
+            self._conv_fused = {length: _cabi.conv1d_supported(weight.dtype, length, c_in, c_out, taps, activation)
+                                for length in lengths}
+            if any(self._conv_fused.values()):
+                self._conv_weight = weight.detach().permute(2, 0, 1).contiguous()
         return self
 
     def activate_shape(self, sequence_length: int) -> "DebertaV2InferenceEncoder":
@@ -394,7 +453,13 @@ class DebertaV2InferenceEncoder(nn.Module):
             state = _output_block(layer.output, fuse_output, inner, mixed)
             if depth == 0 and self.conv is not None:
                 # the convolution branch sees the encoder input and the padding mask as the caller gave it
-                state = self.conv(hidden_states, state, attention_mask)
+                if self._conv_fused.get(hidden_states.size(1), False) and hidden_states.dtype == state.dtype:
+                    norm = self.conv.LayerNorm
+                    state = _conv_branch_op(hidden_states, state, attention_mask, self._conv_weight,
+                                            self.conv.conv.bias, norm.weight, norm.bias, float(norm.eps),
+                                            self._conv_activation_code, self._status_word)
+                else:
+                    state = self.conv(hidden_states, state, attention_mask)
             if trace is not None:
                 trace.append(state)
         collected = None if trace is None else tuple(trace)

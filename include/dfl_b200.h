@@ -265,6 +265,7 @@ DFL_API int dfl_attention_rel_fwd(const DflAttnRelParams* p, void* stream);
  */
 #define DFL_ACT_NONE 0
 #define DFL_ACT_GELU 1
+#define DFL_ACT_TANH 2
 typedef struct DflDenseParams {
   const void* x;        /* [M, K] */
   const void* w;        /* [N, K] (nn.Linear weight layout) */
@@ -277,6 +278,33 @@ typedef struct DflDenseParams {
   int32_t* status;      /* optional device int32, see dfl_check_status() */
 } DflDenseParams;
 DFL_API int dfl_dense(const DflDenseParams* p, void* stream);
+
+/*
+ * 1-D convolution over the sequence with 'same' zero padding, stride 1, one group, as one tensor-core GEMM over the
+ * taps, with bias, padding mask and activation in the epilogue:
+ *     out[b, l, :] = act(keep[b, l] * (bias + sum_t w[t] * x[b, l + t - taps/2, :]))
+ * Replaces, in ConvLayer.forward (_reference.py:534-556), the two permute().contiguous() copies around nn.Conv1d,
+ * the convolution, masked_fill_ and the activation.  x is [batch, seq_len, c_in], w is [taps, c_out, c_in] (the
+ * nn.Conv1d weight [c_out, c_in, taps] permuted once at prepare time), out is [batch, seq_len, c_out]; row_mask is
+ * the [batch, seq_len] padding mask (non-zero = keep) or NULL.  The taps are k-steps of the GEMM: the operand
+ * loads of tap t start t - taps/2 rows higher or lower, and rows outside the sequence read as zero.
+ * Covered: F16/BF16, taps odd and <= 9, seq_len >= 256, c_in >= 64, c_in and c_out multiples of 8;
+ * dfl_conv1d_supported() tells, other configurations return DFL_ERR_UNSUPPORTED.
+ */
+typedef struct DflConv1dParams {
+  const void* x;         /* [batch, seq_len, c_in] */
+  const void* w;         /* [taps, c_out, c_in] */
+  const void* bias;      /* [c_out] or NULL */
+  const void* row_mask;  /* [batch, seq_len] or NULL */
+  void*       out;       /* [batch, seq_len, c_out] */
+  int32_t batch, seq_len, c_in, c_out, taps;
+  int32_t mask_elem_size; /* 1, 4 or 8 */
+  int32_t activation;    /* DFL_ACT_* */
+  int32_t dtype;
+  int32_t* status;       /* optional device int32, see dfl_check_status() */
+} DflConv1dParams;
+DFL_API int dfl_conv1d_supported(const DflConv1dParams* p);
+DFL_API int dfl_conv1d(const DflConv1dParams* p, void* stream);
 
 /*
  * Residual add + LayerNorm in one pass (the tail of a layer's two output blocks):
@@ -300,6 +328,8 @@ typedef struct DflAddLayerNormParams {
   int32_t hidden;
   float   eps;
   int32_t dtype;
+  const void* row_mask;    /* [rows] or NULL: output rows whose element is zero are written as zeros */
+  int32_t mask_elem_size;  /* 1, 4 or 8 */
 } DflAddLayerNormParams;
 DFL_API int dfl_add_layernorm_supported(int dtype, int hidden);
 DFL_API int dfl_add_layernorm(const DflAddLayerNormParams* p, void* stream);
