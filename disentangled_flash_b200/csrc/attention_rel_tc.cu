@@ -410,14 +410,31 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       if (!any_kept) {
         // Every query row of this tile is padding: each attends uniformly to all L keys, so every output row is
         // the column mean of V.  No score, no softmax: one pass over V by the 256 softmax threads.
-        float* part = reinterpret_cast<float*>(smem + LO::offMeanV);         // [groups][D] partial sums
+        // 16-byte loads, every thread sums 8 columns over a stride of rows; the row groups of a warp are folded with
+        // shuffles and the eight warps through shared memory (the row-exchange words are idle during such an item).
+        float* part = xmax;                                                  // [8 warps][D] partial sums
         T* mean = reinterpret_cast<T*>(smem + LO::offMeanV + 1024);          // [D]
-        constexpr int kGroups = 256 / D;
-        const int tid = threadIdx.x, col = tid % D, grp = tid / D;
-        const T* V = reinterpret_cast<const T*>(p.v) + (long long)bh * L * D;
-        float sum = 0.0f;
-        for (int row = grp; row < L; row += kGroups) sum += Elem<T>::to_f(V[(long long)row * D + col]);
-        part[grp * D + col] = sum;
+        constexpr int kChunks = D / 8;             // 16-byte chunks per row of V
+        constexpr int kRowStep = 256 / kChunks;    // rows covered by the 256 threads at once
+        const int tid = threadIdx.x, chunk = tid % kChunks, rgrp = tid / kChunks;
+        const uint4* V4 = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.v) + (long long)bh * L * D);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int row = rgrp; row < L; row += kRowStep) {
+          const uint4 raw = __ldg(V4 + (long long)row * kChunks + chunk);
+          const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += Elem<T>::to_f(e[j]);
+        }
+#pragma unroll
+        for (int o = kChunks; o < 32; o <<= 1) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+        }
+        if (lane < kChunks) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) part[warp * D + lane * 8 + j] = acc[j];
+        }
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&bars->xbar);
         ok = wwait(&bars->xbar, c_xb & 1u, 34);
@@ -425,7 +442,8 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         if (!ok) break;
         if (tid < D) {
           float total = 0.0f;
-          for (int gidx = 0; gidx < kGroups; ++gidx) total += part[gidx * D + tid];
+#pragma unroll
+          for (int w = 0; w < kSoftmaxWarps; ++w) total += part[w * D + tid];
           mean[tid] = Elem<T>::from_f(total / (float)L);
         }
         __syncwarp();
