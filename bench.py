@@ -12,8 +12,9 @@ Workloads (``--workload``; the reference's recipe is benchmarks/benchmark_cuda.p
     its own batch; there is no collective in the forward, NCCL only gathers per-rank checksums after timing (weak
     scaling).  The JSON line reports encoder sequences/s (`value`, inputs resident in HBM), the same through host
     buffers with the copies overlapped on their own streams (`e2e`), the fused attention kernel's TFLOP/s against
-    the measured tensor-core peak (`roofline`, `attention_op`), a host-CPU baseline (`cpu_baseline`), and the
-    batch-sharded v3-large mixed-bucket throughput of `v3-large-mixed` as the extra key `mixed_buckets`.
+    the measured tensor-core peak (`roofline`, `attention_op`), a host-CPU baseline (`cpu_baseline`), the same step
+    replayed as one CUDA graph (`cuda_graph`), and the batch-sharded v3-large mixed-bucket throughput of
+    `v3-large-mixed` as the extra key `mixed_buckets`.
 ``attention-sweep``
     The attention operator alone: (H, d) in {(24,32), (12,64), (8,128)}, B=16, L in {16,64,256,512}, BF16 and FP16,
     a quarter of the rows padded; one row per shape with microseconds, TFLOP/s and the fraction of the burst peak.
@@ -583,6 +584,23 @@ def run_v3_base(args, ctx: GpuContext) -> None:
                         "flops_qk_pv": 4.0 * B * H * L * L * d, "l2": "256 MB flush write between launches"}
         del q, k, v
 
+    # The same step as one CUDA graph per bucket (capture_deberta_buckets): the step's inputs are copied into the
+    # graph's buffers inside the timed region.  An extra key; `value` stays the eager forward.
+    graph = None
+    if not args.skip_graph:
+        import disentangled_flash_b200 as df
+
+        replay = df.capture_deberta_buckets(encoder, args.batch)[seq_len]
+        with torch.inference_mode():
+            for i in range(args.warmup):
+                replay(*dev_batches[i % len(dev_batches)])
+            ms_graph = timed_region(ctx, lambda: [replay(*dev_batches[i % len(dev_batches)]) for i in range(args.steps)])
+        encoder.check_device_status()
+        graph = {"value": seqs / (ms_graph / 1e3), "unit": "sequences/s", "ms_per_step": ms_graph / args.steps,
+                 "note": "capture_deberta_buckets(): one graph launch per step, inputs copied device-to-device into "
+                         "the graph's buffers every step"}
+        del replay
+
     del encoder, dev_batches, dev_hidden
     torch.cuda.empty_cache()
     mixed = None
@@ -606,6 +624,7 @@ def run_v3_base(args, ctx: GpuContext) -> None:
             "attention_tflops": achieved,
             "roofline": roofline,
             "attention_op": attention_op,
+            "cuda_graph": graph,
             "mixed_buckets": mixed,
             "cpu_baseline": baseline,
             "clocks": clocks,
@@ -783,6 +802,7 @@ def main() -> None:
     parser.add_argument("--cpu-sample", type=int, default=2, help="sequences per CPU-baseline step")
     parser.add_argument("--skip-cpu", action="store_true", help="omit the cpu_baseline leg")
     parser.add_argument("--skip-mixed", action="store_true", help="omit the mixed-bucket leg of the default workload")
+    parser.add_argument("--skip-graph", action="store_true", help="omit the CUDA-graph leg of the default workload")
     args = parser.parse_args()
     if args.warmup < 3 and args.impl == "b200":
         args.warmup = 3  # timing rule: at least three warm-up steps
