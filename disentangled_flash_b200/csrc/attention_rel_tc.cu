@@ -508,6 +508,12 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
                 for (int x = 0; x < 16; ++x) cur[16 * j + x] = Pack2<T>::add(cur[16 * j + x], (uint16_t)pv[x]);
               }
+              // the staging tile is read: the converters may fill it for the next tile while the C2P terms of this
+              // chunk, the mask and pass 2 are still to come
+              if (q == 1) {
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&bars->pt_release);
+              }
             }
             if (has_c2p) {
 #pragma unroll
@@ -541,10 +547,7 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           }
           // the ring blocks and the staging tile of this tile are read
           __syncwarp();
-          if (lane == 0) {
-            if (has_c2p) ptx::mbar_arrive(&bars->ring_release);
-            if (has_p2c) ptx::mbar_arrive(&bars->pt_release);
-          }
+          if (lane == 0 && has_c2p) ptx::mbar_arrive(&bars->ring_release);
           const float my_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
           // the row maximum of the tile needs the other half of the keys: exchange through shared memory
           float* xm = xmax + (c_p2 & 1u) * (2 * BM);
