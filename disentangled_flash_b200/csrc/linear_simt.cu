@@ -8,15 +8,16 @@
 // kind, so strict fp32 is FFMA work; its roofline is the fp32 CUDA-core rate.
 //
 // C_z[m,n] = sum_k X_z[m,k] * W_{z % w_mod}[n,k] (+ bias[n]), fp32 accumulate.
-// Tile 64x64x16, 256 threads, 4x4 outputs per thread, operands staged in
-// shared memory as fp32 with the k index outermost so that the inner product
-// reads two conflict-free float4 per k.
+// Tile 128x128x16 (long inner products) or 64x64x16, 256 threads, 8x8 or 4x4 outputs per thread (4-wide groups of
+// rows and of columns, 64 apart), operands staged in shared memory as fp32 with the k index outermost so that the
+// inner product reads conflict-free float4 (four per k for 64 FMAs with the large tile); the next k-block is fetched from global memory into registers while the current one
+// is multiplied.  Every output accumulates its products in ascending k with one fmaf each.
 #include "dfl_common.cuh"
 
 namespace dfl {
 namespace {
 
-constexpr int BM = 64, BN = 64, BK = 16, PAD = 4;
+constexpr int BK = 16, PAD = 4;
 
 template <typename T>
 __device__ __forceinline__ void load4(const T* p, bool vec_ok, int valid, float (&v)[4]) {
@@ -37,9 +38,11 @@ __device__ __forceinline__ void load4(const T* p, bool vec_ok, int valid, float 
   }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(256)
+// G = 4-wide groups of rows and of columns per thread: tile 64*G x 64*G, (4*G)^2 outputs per thread.
+template <typename T, int G>
+__global__ void __launch_bounds__(256, G > 1 ? 2 : 5)
 gemm_simt_kernel(GemmDesc g) {
+  constexpr int BM = 64 * G, BN = 64 * G, R = 4 * G;
   __shared__ float As[BK][BM + PAD];
   __shared__ float Bs[BK][BN + PAD];
 
@@ -50,54 +53,71 @@ gemm_simt_kernel(GemmDesc g) {
   const int tid = threadIdx.x;
   const int ty = tid / 16, tx = tid % 16;
 
-  // loader mapping: one 4-element k-run of one row per thread, for A and for B
+  // loader mapping: two 4-element k-runs (rows lrow and lrow + 64) per thread, for A and for B
   const int lrow = tid / 4, lk = (tid % 4) * 4;
   // vector loads need K % 4 == 0 (row starts stay aligned) and an aligned base
   const bool vec_ok = (g.K % 4 == 0) && ((reinterpret_cast<uintptr_t>(X) % (4 * sizeof(T))) == 0) &&
                       ((reinterpret_cast<uintptr_t>(W) % (4 * sizeof(T))) == 0);
 
-  float acc[4][4];
+  float acc[R][R];
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < R; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    for (int j = 0; j < R; ++j) acc[i][j] = 0.0f;
 
-  for (int k0 = 0; k0 < g.K; k0 += BK) {
-    float a[4], b[4];
+  float a[G][4], b[G][4];
+  auto fetch = [&](int k0) {
     const int kk = k0 + lk;
     const int kvalid = g.K - kk < 0 ? 0 : (g.K - kk > 4 ? 4 : g.K - kk);
-    const int am = m0 + lrow, bn = n0 + lrow;
-    load4<T>(X + (long long)am * g.K + kk, vec_ok, am < g.M ? kvalid : 0, a);
-    load4<T>(W + (long long)bn * g.K + kk, vec_ok, bn < g.N ? kvalid : 0, b);
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+      const int am = m0 + lrow + 64 * h, bn = n0 + lrow + 64 * h;
+      load4<T>(X + (long long)am * g.K + kk, vec_ok, am < g.M ? kvalid : 0, a[h]);
+      load4<T>(W + (long long)bn * g.K + kk, vec_ok, bn < g.N ? kvalid : 0, b[h]);
+    }
+  };
+  // the large tile fetches the next k-block while it multiplies; the small tile, used for short inner products,
+  // keeps its registers for occupancy instead
+  constexpr bool kPrefetch = G > 1;
+  if (kPrefetch) fetch(0);
+  for (int k0 = 0; k0 < g.K; k0 += BK) {
+    if (!kPrefetch) fetch(k0);
     __syncthreads();  // previous tile fully consumed
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      As[lk + i][lrow] = a[i];
-      Bs[lk + i][lrow] = b[i];
-    }
+    for (int h = 0; h < G; ++h)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        As[lk + i][lrow + 64 * h] = a[h][i];
+        Bs[lk + i][lrow + 64 * h] = b[h][i];
+      }
     __syncthreads();
+    if (kPrefetch && k0 + BK < g.K) fetch(k0 + BK);   // in flight during the multiply
 #pragma unroll
     for (int k = 0; k < BK; ++k) {
-      const float4 av = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
-      const float4 bv = *reinterpret_cast<const float4*>(&Bs[k][tx * 4]);
-      const float ar[4] = {av.x, av.y, av.z, av.w};
-      const float br[4] = {bv.x, bv.y, bv.z, bv.w};
+      float ar[R], br[R];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int h = 0; h < G; ++h) {
+        const float4 av = *reinterpret_cast<const float4*>(&As[k][64 * h + ty * 4]);
+        const float4 bv = *reinterpret_cast<const float4*>(&Bs[k][64 * h + tx * 4]);
+        ar[4 * h] = av.x; ar[4 * h + 1] = av.y; ar[4 * h + 2] = av.z; ar[4 * h + 3] = av.w;
+        br[4 * h] = bv.x; br[4 * h + 1] = bv.y; br[4 * h + 2] = bv.z; br[4 * h + 3] = bv.w;
+      }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(ar[i], br[j], acc[i][j]);
+      for (int i = 0; i < R; ++i)
+#pragma unroll
+        for (int j = 0; j < R; ++j) acc[i][j] = fmaf(ar[i], br[j], acc[i][j]);
     }
   }
 
-  // epilogue
+  // epilogue: rows ty*4 + i and 64 + ty*4 + i, columns tx*4 + j and 64 + tx*4 + j
   const T* bias = reinterpret_cast<const T*>(g.bias);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int m = m0 + ty * 4 + i;
+  for (int i = 0; i < R; ++i) {
+    const int m = m0 + (i >> 2) * 64 + ty * 4 + (i & 3);
     if (m >= g.M) continue;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int n = n0 + tx * 4 + j;
+    for (int j = 0; j < R; ++j) {
+      const int n = n0 + (j >> 2) * 64 + tx * 4 + (j & 3);
       if (g.head_split) {
         if (n >= g.N) continue;
         float v = acc[i][j];
@@ -105,9 +125,9 @@ gemm_simt_kernel(GemmDesc g) {
         const int hd = g.heads * g.head_dim;
         const int which = n / hd, rem = n % hd;
         const int h = rem / g.head_dim, dd = rem % g.head_dim;
-        const int b = m / g.rows_per_seq, l = m % g.rows_per_seq;
+        const int b_ = m / g.rows_per_seq, l = m % g.rows_per_seq;
         T* out = reinterpret_cast<T*>(g.out[which]);
-        out[(((long long)b * g.heads + h) * g.rows_per_seq + l) * g.head_dim + dd] = Elem<T>::from_f(v);
+        out[(((long long)b_ * g.heads + h) * g.rows_per_seq + l) * g.head_dim + dd] = Elem<T>::from_f(v);
       } else {
         if (n >= g.ldc) continue;
         float v = n < g.N ? acc[i][j] : 0.0f;
@@ -122,14 +142,23 @@ gemm_simt_kernel(GemmDesc g) {
 
 }  // namespace
 
-int launch_gemm_simt(const GemmDesc& g, cudaStream_t stream) {
+template <int G>
+int launch_tiles(const GemmDesc& g, cudaStream_t stream) {
   const int ncols = g.head_split ? g.N : g.ldc;
-  dim3 grid((ncols + BN - 1) / BN, (g.M + BM - 1) / BM, g.batch);
+  constexpr int TILE = 64 * G;
+  dim3 grid((ncols + TILE - 1) / TILE, (g.M + TILE - 1) / TILE, g.batch);
   if (grid.y > 65535 || grid.z > 65535) return fail(DFL_ERR_TOO_LARGE, "gemm_simt grid too large");
-  if (g.dtype == DFL_F32) gemm_simt_kernel<float><<<grid, 256, 0, stream>>>(g);
-  else if (g.dtype == DFL_F16) gemm_simt_kernel<__half><<<grid, 256, 0, stream>>>(g);
-  else gemm_simt_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(g);
+  if (g.dtype == DFL_F32) gemm_simt_kernel<float, G><<<grid, 256, 0, stream>>>(g);
+  else if (g.dtype == DFL_F16) gemm_simt_kernel<__half, G><<<grid, 256, 0, stream>>>(g);
+  else gemm_simt_kernel<__nv_bfloat16, G><<<grid, 256, 0, stream>>>(g);
   return check_launch("gemm_simt_kernel");
+}
+
+int launch_gemm_simt(const GemmDesc& g, cudaStream_t stream) {
+  // 128 x 128 tiles for long inner products (the projections), 64 x 64 for the short ones (position scores, K = d)
+  // and for outputs too small to fill the GPU with large tiles
+  const long long big_tiles = (long long)((g.M + 127) / 128) * (((g.head_split ? g.N : g.ldc) + 127) / 128) * g.batch;
+  return g.K >= 256 && big_tiles >= 64 ? launch_tiles<2>(g, stream) : launch_tiles<1>(g, stream);
 }
 
 }  // namespace dfl
