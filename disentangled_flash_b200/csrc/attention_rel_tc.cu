@@ -733,18 +733,22 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     auto convert_half = [&](int half) -> bool {
       if (!wwait(&bars->xp_full, c_xp & 1u, 19)) return false;
       ptx::tc_fence_after();
+      // A warp's 32 keys reach chunks 4*q4 .. 4*q4 + 19 of the window's 32: quarters 2 and 3 never store anything of
+      // the first 64 columns of the first half, quarters 0 and 1 nothing of the last 64 of the second half.
+      const int p_begin = (half == 0 && q4 >= 2) ? 1 : 0;
+      const int p_end = (half == 1 && q4 <= 1) ? 1 : 2;
 #pragma unroll 1
-      for (int piece = 0; piece < 2; ++piece) {
+      for (int piece = p_begin; piece < p_end; ++piece) {
         uint32_t r0[32], r1[32];
         ptx::tmem_ld32(t_xp + piece * 64, r0);
         ptx::tmem_ld32(t_xp + piece * 64 + 32, r1);
         ptx::tmem_wait_ld();
-        if (piece == 1) {   // the half is in registers: the accumulator is free for the next half's MMA
+        if (piece == p_end - 1) {   // what this warp needs of the half is in registers: its share of xp_free
           ptx::tc_fence_before();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(&bars->xp_free);
         }
-        if (half == 0 && piece == 0) {
+        if (half == 0 && piece == p_begin) {
           // the staging tile must have been read by all softmax warps (previous tile)
           if (!wwait(&bars->pt_release, (c_pt & 1u) ^ 1u, 20)) return false;
         }
