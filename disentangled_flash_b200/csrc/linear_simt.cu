@@ -156,9 +156,9 @@ int launch_tiles(const GemmDesc& g, cudaStream_t stream) {
 
 int launch_gemm_simt(const GemmDesc& g, cudaStream_t stream) {
   // 128 x 128 tiles for long inner products (the projections), 64 x 64 for the short ones (position scores, K = d)
-  // and for outputs too small to fill the GPU with large tiles
+  // and for outputs too small to give every SM two of the large tiles (296 on a 148-SM part)
   const long long big_tiles = (long long)((g.M + 127) / 128) * (((g.head_split ? g.N : g.ldc) + 127) / 128) * g.batch;
-  return g.K >= 256 && big_tiles >= 64 ? launch_tiles<2>(g, stream) : launch_tiles<1>(g, stream);
+  return g.K >= 256 && big_tiles >= 296 ? launch_tiles<2>(g, stream) : launch_tiles<1>(g, stream);
 }
 
 }  // namespace dfl
