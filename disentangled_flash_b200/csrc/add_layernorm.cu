@@ -103,6 +103,7 @@ add_layernorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ resi
   const float inv_n = 1.0f / (float)hidden;
   const long long warp0 = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   const long long stride = (long long)gridDim.x * kWarpsPerBlock;
+  wait_for_predecessor();
   for (long long row = warp0; row < rows; row += stride) {
     const uint4* xr = x + row * vecs_per_row;
     const uint4* rr = residual ? residual + row * vecs_per_row : nullptr;
@@ -170,9 +171,9 @@ void launch_one(const void* x, const void* residual, const void* gamma, const vo
   const long long wanted = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
   const long long cap = (long long)sm_count * 8;   // 8 CTAs of 8 warps per SM: one wave, grid-stride beyond it
   const int blocks = (int)(wanted < cap ? wanted : cap);
-  add_layernorm_kernel<T, VEC><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
-      (const uint4*)x, (const uint4*)residual, (const uint4*)gamma, (const uint4*)beta, (uint4*)out, rows, hidden, eps,
-      row_mask, mask_elem);
+  launch_after_predecessor(add_layernorm_kernel<T, VEC>, dim3(blocks), dim3(kWarpsPerBlock * 32), 0, stream,
+                           (const uint4*)x, (const uint4*)residual, (const uint4*)gamma, (const uint4*)beta, (uint4*)out,
+                           rows, hidden, eps, row_mask, mask_elem);
 }
 
 template <typename T>

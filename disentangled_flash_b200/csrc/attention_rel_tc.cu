@@ -369,6 +369,10 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     return __all_sync(0xffffffffu, ptx::mbar_wait_inline(bar, parity, abort_flag, fail_code, code));
   };
 
+  // The set-up above overlaps the tail of the previous kernel of the stream; Q, K, V, the mask and the status word
+  // are touched from here on.
+  wait_for_predecessor();
+
   // Every role walks the same item sequence (item number k of this CTA is item blockIdx.x + k * gridDim.x; it uses
   // item slot k % 3 in phase (k / 3) & 1) and keeps its own running counters.  Register budgets are set per
   // warpgroup (warps 0-3, 4-7: softmax; 8-11: converters; 12-15: the rest), at the head of the branch the whole
@@ -1172,7 +1176,9 @@ int launch_rel_typed(const DflAttnRelParams& p, cudaStream_t stream) {
   const long long n_items = (long long)BH * ((L + BM - 1) / BM);
   if (n_items > 0x7fffffffLL) return fail(DFL_ERR_TOO_LARGE, "too many (batch, head, query tile) items");
   const int grid = n_items < sm_count ? (int)n_items : sm_count;
-  kernel<<<grid, kThreads, LO::total, stream>>>(tq, tk, tv, tfk, tfq, p, status_word, (int)n_items);
+  e = launch_after_predecessor(kernel, dim3(grid), dim3(kThreads), LO::total, stream, tq, tk, tv, tfk, tfq, p, status_word,
+                               (int)n_items);
+  if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "attention_rel_kernel: %s", cudaGetErrorString(e));
   return check_launch("attention_rel_kernel");
 }
 

@@ -69,6 +69,29 @@ inline int configure_kernel(KernelDeviceConfig& cfg, Kernel kernel, int smem_byt
   return DFL_OK;
 }
 
+// Launch with programmatic stream serialization: the kernel's CTAs may be scheduled, and run up to their
+// `griddepcontrol.wait`, while the previous kernel of the stream is still draining; everything that touches global
+// memory comes after that wait, which returns when the previous kernel has completed and its writes are visible.
+// This takes the launch latency and the kernel's set-up (barrier initialisation, tensor-memory allocation, descriptor
+// prefetch) off the path between two dependent kernels.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_after_predecessor(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                            cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+// Device side of the above: wait for the previous kernel of the stream (no-op for a plain launch).
+__device__ __forceinline__ void wait_for_predecessor() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline size_t dtype_size(int dtype) { return dtype == DFL_F32 ? 4 : 2; }

@@ -432,6 +432,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
   ptx::cluster_sync_all();   // the peer's barriers exist before anything is reported to them
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  wait_for_predecessor();    // the set-up above overlaps the previous kernel's tail; its outputs are read from here on
 
   auto tile_coords = [&](int tile, int& m0, int& n0, int& z) {
     const int per_z = tiles_n * tiles_m;
@@ -596,8 +597,9 @@ int launch_pair(const GemmDesc& g, cudaStream_t stream) {
   const long long max_pairs = num_sms / 2;
   const int pairs = (int)(num_tiles < max_pairs ? num_tiles : max_pairs);
   const int num_kb = taps * ((g.K + BK - 1) / BK);
-  kernel<<<2 * pairs, kThreads, kPairSmem, stream>>>(tmap_x, tmap_w, tmap_out, gd, num_kb, tiles_n, tiles_m,
-                                                     (int)num_tiles, tiled);
+  cudaError_t le = launch_after_predecessor(kernel, dim3(2 * pairs), dim3(kThreads), kPairSmem, stream, tmap_x, tmap_w,
+                                            tmap_out, gd, num_kb, tiles_n, tiles_m, (int)num_tiles, tiled);
+  if (le != cudaSuccess) return fail(DFL_ERR_LAUNCH, "gemm_tc_pair_kernel: %s", cudaGetErrorString(le));
   return check_launch("gemm_tc_pair_kernel");
 }
 
