@@ -26,6 +26,10 @@ Workloads (``--workload``; the reference's recipe is benchmarks/benchmark_cuda.p
     sequences in three buckets (171 / 171 / 170 at L = 128 / 256 / 512) sharded over the ranks with
     ``sharding.shard_buckets``; sequences/s = 512 / the slowest rank's time (strong scaling).
 
+Timing: W warm-up steps (at least 3), then regions of exactly K steps between a barrier + synchronize on both sides,
+CUDA events on the launching stream, maximum over ranks.  The region is run twice and the faster run is reported
+(shared hosts: a stalled launching thread can double a 100 ms region); both times are in ``timed_runs_ms``.
+
 ``--impl reference`` times the reference's own PyTorch backend on the host CPU cores (from ``oracle/_ref``, staged by
 ``oracle/build_ref.py``; the CPU restatement in ``oracle/`` if that copy is absent) on a bounded sample of the
 workload; under torchrun only rank 0 runs it.
@@ -521,14 +525,20 @@ def run_v3_base(args, ctx: GpuContext) -> None:
         for i in range(args.warmup):
             step_resident(i)
         run_e2e(args.warmup)
+        # The timed region (exactly K steps between two barriers) is run twice and the faster run is reported, for
+        # `value` and for `e2e` alike: these hosts are shared, and a stall of the launching thread for a few tens of
+        # milliseconds doubles a 100 ms region.  Both times are in the JSON line (`timed_runs_ms`).
         observer.enabled = True
-        torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see exactly the timed region
-        ms_total = timed_region(ctx, lambda: [step_resident(i) for i in range(args.steps)], sampler)
+        torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see exactly one timed region
+        runs_resident = [timed_region(ctx, lambda: [step_resident(i) for i in range(args.steps)], sampler)]
         torch.cuda.profiler.stop()
         observer.enabled = False
+        launches_per_run = observer.launches
         clocks = sampler.stop()
         attn_ms = [s.elapsed_time(e) for s, e in observer.events]
-        ms_e2e = timed_region(ctx, lambda: run_e2e(args.steps))
+        runs_resident.append(timed_region(ctx, lambda: [step_resident(i) for i in range(args.steps)]))
+        runs_e2e = [timed_region(ctx, lambda: run_e2e(args.steps)) for _ in range(2)]
+        ms_total, ms_e2e = min(runs_resident), min(runs_e2e)
         last = step_resident(0)
         checksum = last.float().abs().mean().reshape(1)
     encoder.check_device_status()
@@ -620,7 +630,9 @@ def run_v3_base(args, ctx: GpuContext) -> None:
             "e2e": {"value": e2e_value, "unit": "sequences/s", "h2d_bytes_per_step": bytes_in,
                     "d2h_bytes_per_step": bytes_out, "ms_per_step": ms_e2e / args.steps,
                     "note": "pinned host buffers; input copy, forward and read-back on three streams, two device slots"},
-            "gpu_launches": observer.launches,
+            "gpu_launches": launches_per_run,
+            "timed_runs_ms": {"resident": runs_resident, "e2e": runs_e2e,
+                              "rule": "two runs of exactly K steps each; the faster one is reported"},
             "attention_tflops": achieved,
             "roofline": roofline,
             "attention_op": attention_op,
