@@ -119,6 +119,48 @@ def test_config2_attention_operator_at_benchmark_shape():
     check("config2 operator B32 H12 L512 d64 fp16 lengths U[256,512]", got, oracle_core(case), torch.float16)
 
 
+def test_config2_encoder_at_benchmark_geometry():
+    """The whole 12-layer encoder of the benchmark (v3-base geometry, conv 3, FP16, L=512, lengths U[256,512]) on four
+    sequences against the fp32 CPU oracle encoder run on the FP16-rounded weights: every fused block of the wrapper
+    (QKV and FFN-in GEMMs, attention, add + LayerNorm, convolution branch) at its benchmark shape.  Twelve layers of
+    FP16 activations against an fp32 reference: the bound is on valid tokens, 4e-2 absolute on outputs of unit scale
+    (layer-normed), with a mean error below 2e-3."""
+
+    import hf_modules
+    import disentangled_flash_b200 as df
+    from oracle.encoder import oracle_encoder_forward
+
+    cfg = df.DebertaAttentionConfig(hidden_size=768, num_attention_heads=12, attention_head_size=64,
+                                    num_hidden_layers=12, intermediate_size=3072, max_position_embeddings=512,
+                                    position_buckets=256, norm_rel_ebd="layer_norm", conv_kernel_size=3)
+    reference = hf_modules.Backbone(cfg, vocab_size=8).eval()
+    hf_modules.initialize_parameters(reference, 17)
+    rounded = {k: v.to(torch.float16).float() for k, v in reference.state_dict().items()}
+    backbone = hf_modules.Backbone(cfg, vocab_size=8).eval()
+    backbone.load_state_dict(rounded)
+    backbone = backbone.to(dev, torch.float16)
+    df.optimize_deberta(backbone, sequence_lengths=[512])
+    encoder = backbone.encoder
+    assert encoder._fused_output_blocks == [(True, True)] * 12 and encoder._fused_intermediates == [True] * 12
+    assert encoder._conv_fused == {512: True}
+    gen = torch.Generator().manual_seed(22)
+    hidden = torch.empty(4, 512, 768).normal_(0.0, 0.02, generator=gen).to(torch.float16)   # embedding-row statistics
+    lengths = torch.randint(256, 513, (4,), generator=gen)
+    mask = torch.arange(512)[None, :] < lengths[:, None]
+    with torch.inference_mode():
+        got = encoder(hidden.to(dev), mask.to(dev)).last_hidden_state.float().cpu()
+    encoder.check_device_status()
+    reference.load_state_dict(rounded)
+    want = oracle_encoder_forward(reference, cfg, hidden.float(), mask)
+    assert torch.isfinite(got).all()
+    err = (got - want).abs()[mask]          # valid tokens
+    REPORT["config2 encoder 12 layers B4 L512 fp16 lengths U[256,512]"] = {
+        "max_abs_err": err.max().item(), "mean_abs_err": err.mean().item(), "max_abs_ref": want[mask].abs().max().item(),
+        "bare_bound": 2e-3, "within_bare_bound": bool((err <= 2e-3).all()), "elements": int(err.numel()),
+        "elements_over_bound": int((err > 4e-2).sum()), "worst_err_over_bound": err.max().item() / 4e-2}
+    assert err.max().item() <= 4e-2 and err.mean().item() <= 2e-3, (err.max().item(), err.mean().item())
+
+
 # ------------------------------------------------------------------ config 4: head-dim sweep
 SWEEP_GEOMETRY = ((24, 32), (12, 64), (8, 128))
 SWEEP_LENGTHS = (16, 64, 256, 512)
