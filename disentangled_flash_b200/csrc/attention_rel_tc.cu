@@ -50,6 +50,15 @@ constexpr int kThreads = 512;
 constexpr int kSoftmaxRegs = 152;    // 256 x 152 + 128 x 120 + 128 x 88 = 65536 registers
 constexpr int kConvRegs = 120;
 constexpr int kMiscRegs = 88;
+// The kernel is launched with 65536 / kThreads = 128 registers per thread.  `setmaxnreg.inc` waits until the pool
+// holds what it asks for, so the three budgets must not ask for more than the SM has (a wait that nothing could
+// bound); `setmaxnreg.dec` with a value above the launch allocation is an illegal instruction.
+constexpr int kLaunchRegs = 65536 / kThreads;
+static_assert(8 * 32 * kSoftmaxRegs + 4 * 32 * kConvRegs + 4 * 32 * kMiscRegs <= kThreads * kLaunchRegs,
+              "register budgets of the three warpgroup kinds exceed what the launch allocates");
+static_assert(kSoftmaxRegs >= kLaunchRegs && kConvRegs <= kLaunchRegs && kMiscRegs <= kLaunchRegs &&
+                  kSoftmaxRegs % 8 == 0 && kConvRegs % 8 == 0 && kMiscRegs % 8 == 0,
+              "setmaxnreg.inc raises and setmaxnreg.dec lowers the launch allocation, in multiples of 8");
 constexpr int kConsumerWarps = 13;   // softmax, converters, MMA issuer: every warp that reads an item slot
 
 constexpr int kItemSlots = 3;        // the loader analyses one item ahead of the one whose tiles it loads
