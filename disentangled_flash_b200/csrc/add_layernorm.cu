@@ -84,9 +84,11 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-__device__ __forceinline__ uint4 ld_stream(const uint4* p) {   // read once: do not keep in L1
+// Read once: do not keep in L1.  A plain (coherent) load: `out` may be the same buffer as `x` or `residual`, so the
+// inputs are not read-only for the lifetime of the kernel.
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
@@ -94,8 +96,8 @@ __device__ __forceinline__ uint4 ld_stream(const uint4* p) {   // read once: do 
 // Vector j of lane l covers columns (j*32 + l) * E .. +E: a warp reads 512 contiguous bytes per vector index.
 template <typename T, int VEC>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-add_layernorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ residual, const uint4* __restrict__ gamma,
-                     const uint4* __restrict__ beta, uint4* __restrict__ out, long long rows, int hidden, float eps,
+add_layernorm_kernel(const uint4* x, const uint4* residual, const uint4* __restrict__ gamma,
+                     const uint4* __restrict__ beta, uint4* out, long long rows, int hidden, float eps,
                      const void* __restrict__ row_mask, int mask_elem) {
   constexpr int E = Vec16<T>::kElems;
   const int lane = threadIdx.x & 31;
