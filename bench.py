@@ -13,7 +13,8 @@ Workloads (``--workload``; the reference's recipe is benchmarks/benchmark_cuda.p
     scaling).  The JSON line reports encoder sequences/s (`value`, inputs resident in HBM), the same through host
     buffers with the copies overlapped on their own streams (`e2e`), the fused attention kernel's TFLOP/s against
     the measured tensor-core peak (`roofline`, `attention_op`), a host-CPU baseline (`cpu_baseline`), the same step
-    replayed as one CUDA graph (`cuda_graph`), and the batch-sharded v3-large mixed-bucket throughput of
+    replayed as one CUDA graph (`cuda_graph`), the same batches run without their padding (`packed`), and the
+    batch-sharded v3-large mixed-bucket throughput of
     `v3-large-mixed` as the extra key `mixed_buckets`.
 ``attention-sweep``
     The attention operator alone: (H, d) in {(24,32), (12,64), (8,128)}, B=16, L in {16,64,256,512}, BF16 and FP16,
@@ -611,6 +612,27 @@ def run_v3_base(args, ctx: GpuContext) -> None:
                          "the graph's buffers every step"}
         del replay
 
+    # The same batches without their padding between the attention kernels (forward_packed; lengths known on the
+    # host as a tokenizer gives them).  Outputs equal `value`'s at the valid positions only, hence an extra key.
+    packed = None
+    if not args.skip_packed:
+        host_lengths = [m.sum(1).tolist() for m in host_mask]
+
+        def step_packed(i):
+            j = i % len(dev_batches)
+            return encoder.forward_packed(dev_batches[j][0], dev_batches[j][1], host_lengths[j]).last_hidden_state
+
+        with torch.inference_mode():
+            for i in range(args.warmup):
+                step_packed(i)
+            ms_packed = min(timed_region(ctx, lambda: [step_packed(i) for i in range(args.steps)]) for _ in range(2))
+        encoder.check_device_status()
+        kept = sum(min(seq_len, -(-n // 32) * 32) for n in host_lengths[0]) / float(args.batch * seq_len)
+        packed = {"value": seqs / (ms_packed / 1e3), "unit": "sequences/s", "ms_per_step": ms_packed / args.steps,
+                  "rows_kept": kept,
+                  "note": "forward_packed(): dense layers, GELU and layer norms on the valid positions only (each "
+                          "sequence rounded up to 32 rows); equal to the padded forward at valid positions"}
+
     del encoder, dev_batches, dev_hidden
     torch.cuda.empty_cache()
     mixed = None
@@ -637,6 +659,7 @@ def run_v3_base(args, ctx: GpuContext) -> None:
             "roofline": roofline,
             "attention_op": attention_op,
             "cuda_graph": graph,
+            "packed": packed,
             "mixed_buckets": mixed,
             "cpu_baseline": baseline,
             "clocks": clocks,
@@ -815,6 +838,7 @@ def main() -> None:
     parser.add_argument("--skip-cpu", action="store_true", help="omit the cpu_baseline leg")
     parser.add_argument("--skip-mixed", action="store_true", help="omit the mixed-bucket leg of the default workload")
     parser.add_argument("--skip-graph", action="store_true", help="omit the CUDA-graph leg of the default workload")
+    parser.add_argument("--skip-packed", action="store_true", help="omit the packed-rows leg of the default workload")
     args = parser.parse_args()
     if args.warmup < 3 and args.impl == "b200":
         args.warmup = 3  # timing rule: at least three warm-up steps

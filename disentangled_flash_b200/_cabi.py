@@ -42,6 +42,7 @@ EXPORTED_SYMBOLS = (
     "dfl_add_layernorm",
     "dfl_dense",
     "dfl_conv1d",
+    "dfl_copy_rows",
     "dfl_conv1d_supported",
     "dfl_add_layernorm_supported",
     "dfl_pos_scores",
@@ -97,6 +98,7 @@ class DflAttnRelParams(Structure):
         ("mask", c_void_p), ("out", c_void_p), ("status", c_void_p),
         ("batch", c_int32), ("heads", c_int32), ("seq_len", c_int32), ("head_dim", c_int32),
         ("mask_elem_size", c_int32), ("scale", c_float), ("dtype", c_int32), ("algo", c_int32),
+        ("out_row_base", c_void_p), ("out_row_count", c_void_p),
     ]
 
 
@@ -118,7 +120,7 @@ class DflConv1dParams(Structure):
 class DflAddLayerNormParams(Structure):
     _fields_ = [("x", c_void_p), ("residual", c_void_p), ("gamma", c_void_p), ("beta", c_void_p), ("out", c_void_p),
                 ("rows", ctypes.c_int64), ("hidden", c_int), ("eps", ctypes.c_float), ("dtype", c_int),
-                ("row_mask", c_void_p), ("mask_elem_size", c_int)]
+                ("row_mask", c_void_p), ("mask_elem_size", c_int), ("out2", c_void_p), ("out2_rows", c_void_p)]
 
 
 class DflError(RuntimeError):
@@ -159,6 +161,8 @@ def load_library() -> ctypes.CDLL:
     lib.dfl_conv1d_supported.argtypes = [POINTER(DflConv1dParams)]
     lib.dfl_conv1d.restype = c_int
     lib.dfl_conv1d.argtypes = [POINTER(DflConv1dParams), c_void_p]
+    lib.dfl_copy_rows.restype = c_int
+    lib.dfl_copy_rows.argtypes = [c_void_p, c_void_p, c_void_p, ctypes.c_int64, c_int32, c_void_p]
     lib.dfl_dense.restype = c_int
     lib.dfl_dense.argtypes = [POINTER(DflDenseParams), c_void_p]
     lib.dfl_add_layernorm_supported.restype = c_int
@@ -378,10 +382,30 @@ def conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, row
     return out
 
 
+def copy_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[r] = src2d[rows[r]]`` (zeros where ``rows[r] < 0``); ``src`` is read as a matrix of its last dimension."""
+
+    lib = load_library()
+    _require_cuda_contiguous("src", src)
+    _require_cuda_contiguous("rows", rows)
+    if rows.dtype != torch.int32:
+        raise TypeError("rows must be int32")
+    width = src.shape[-1]
+    row_bytes = width * src.element_size()
+    if out is None:
+        out = torch.empty(rows.numel(), width, dtype=src.dtype, device=src.device)
+    with torch.cuda.device(src.device):
+        _check(lib.dfl_copy_rows(src.data_ptr(), out.data_ptr(), rows.data_ptr(), rows.numel(), row_bytes,
+                                 _stream(src.device)), "dfl_copy_rows")
+    return out
+
+
 def add_layernorm(x: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor | None,
-                  eps: float, out: torch.Tensor | None = None, row_mask: torch.Tensor | None = None) -> torch.Tensor:
+                  eps: float, out: torch.Tensor | None = None, row_mask: torch.Tensor | None = None,
+                  scatter: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:
     """``LayerNorm(x + residual) * weight + bias`` over the last dimension, sum and statistics in fp32; rows whose
-    ``row_mask`` element is zero are written as zeros."""
+    ``row_mask`` element is zero are written as zeros.  ``scatter = (out2, rows)`` also writes row ``r`` of the
+    result to row ``rows[r]`` of ``out2`` (skipped where negative)."""
 
     lib = load_library()
     hidden = x.shape[-1]
@@ -405,6 +429,13 @@ def add_layernorm(x: torch.Tensor, residual: torch.Tensor | None, weight: torch.
         if row_mask.numel() != p.rows:
             raise ValueError("row_mask must have one element per row of x")
         p.row_mask, p.mask_elem_size = _ptr(row_mask), row_mask.element_size()
+    if scatter is not None:
+        out2, out2_rows = scatter
+        _require_cuda_contiguous("out2", out2)
+        _require_cuda_contiguous("out2_rows", out2_rows)
+        if out2.dtype != x.dtype or out2.shape[-1] != hidden or out2_rows.dtype != torch.int32 or out2_rows.numel() != p.rows:
+            raise ValueError("scatter = (out2 [*, hidden] in the dtype of x, rows int32 [rows of x])")
+        p.out2, p.out2_rows = _ptr(out2), _ptr(out2_rows)
     with torch.cuda.device(x.device):
         _check(lib.dfl_add_layernorm(ctypes.byref(p), _stream(x.device)), "dfl_add_layernorm")
     return out
@@ -532,8 +563,12 @@ def attention_rel_supported(dtype: torch.dtype, seq_len: int, head_dim: int, has
 
 def attention_rel_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rel_key: torch.Tensor | None,
                       rel_query: torch.Tensor | None, mask: torch.Tensor, scale: float, *,
-                      status: torch.Tensor | None = None) -> torch.Tensor:
-    """Fused attention over position tables laid out by relative distance ([H, 2L-1, d])."""
+                      status: torch.Tensor | None = None, packed_rows: tuple[torch.Tensor, torch.Tensor, int] | None = None
+                      ) -> torch.Tensor:
+    """Fused attention over position tables laid out by relative distance ([H, 2L-1, d]).
+
+    ``packed_rows = (row_base int32[B], row_count int32[B], total_rows)`` selects the packed output ``[T, H*d]``:
+    sequence ``b`` owns rows ``row_base[b] .. + row_count[b]``."""
 
     lib = load_library()
     for name, t in (("q", q), ("k", k), ("v", v), ("mask", mask)):
@@ -546,8 +581,17 @@ def attention_rel_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rel_key
                 raise ValueError(f"{name} must be [H, 2L-1, d] in the dtype of q")
     if mask.element_size() not in (1, 4, 8) or mask.dtype.is_floating_point:
         raise TypeError("mask must be a bool or integer tensor")
-    out = torch.empty(bsz, length, heads * d, dtype=q.dtype, device=q.device)
     p = DflAttnRelParams()
+    if packed_rows is None:
+        out = torch.empty(bsz, length, heads * d, dtype=q.dtype, device=q.device)
+    else:
+        row_base, row_count, total_rows = packed_rows
+        for name, t in (("row_base", row_base), ("row_count", row_count)):
+            _require_cuda_contiguous(name, t)
+            if t.dtype != torch.int32 or t.numel() != bsz:
+                raise ValueError(f"{name} must be int32 [B]")
+        out = torch.empty(total_rows, heads * d, dtype=q.dtype, device=q.device)
+        p.out_row_base, p.out_row_count = row_base.data_ptr(), row_count.data_ptr()
     p.q, p.k, p.v, p.rel_key, p.rel_query = q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(rel_key), _ptr(rel_query)
     p.mask, p.out, p.status = mask.data_ptr(), out.data_ptr(), _ptr(status)
     p.batch, p.heads, p.seq_len, p.head_dim = bsz, heads, length, d

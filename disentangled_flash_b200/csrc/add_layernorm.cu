@@ -98,7 +98,8 @@ template <typename T, int VEC>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 add_layernorm_kernel(const uint4* x, const uint4* residual, const uint4* __restrict__ gamma,
                      const uint4* __restrict__ beta, uint4* out, long long rows, int hidden, float eps,
-                     const void* __restrict__ row_mask, int mask_elem) {
+                     const void* __restrict__ row_mask, int mask_elem, uint4* out2,
+                     const int32_t* __restrict__ out2_rows) {
   constexpr int E = Vec16<T>::kElems;
   const int lane = threadIdx.x & 31;
   const int vecs_per_row = hidden / E;
@@ -152,6 +153,10 @@ add_layernorm_kernel(const uint4* x, const uint4* residual, const uint4* __restr
     const float keep = row_mask && !mask_keep(row_mask, mask_elem, row) ? 0.0f : 1.0f;
     const float rstd = rsqrtf(warp_sum(sq) * inv_n + eps) * keep;
     uint4* orow = out + row * vecs_per_row;
+    // optional second copy of the row at another row index (the unpacked layout of a packed batch)
+    long long row2 = -1;
+    if (out2) row2 = out2_rows[row];
+    uint4* orow2 = row2 >= 0 ? out2 + row2 * vecs_per_row : nullptr;
 #pragma unroll
     for (int j = 0; j < VEC; ++j) {
       const int c = j * 32 + lane;
@@ -161,7 +166,9 @@ add_layernorm_kernel(const uint4* x, const uint4* residual, const uint4* __restr
         if (beta) unpack<T>(__ldg(beta + c), b);
 #pragma unroll
         for (int e = 0; e < E; ++e) y[e] = fmaf((v[j * E + e] - mean) * rstd, g[e], beta ? b[e] * keep : 0.f);
-        orow[c] = pack<T>(y);
+        const uint4 packed = pack<T>(y);
+        orow[c] = packed;
+        if (orow2) orow2[c] = packed;
       }
     }
   }
@@ -169,23 +176,26 @@ add_layernorm_kernel(const uint4* x, const uint4* residual, const uint4* __restr
 
 template <typename T, int VEC>
 void launch_one(const void* x, const void* residual, const void* gamma, const void* beta, void* out, long long rows,
-                int hidden, float eps, const void* row_mask, int mask_elem, int sm_count, cudaStream_t stream) {
+                int hidden, float eps, const void* row_mask, int mask_elem, void* out2, const int32_t* out2_rows,
+                int sm_count, cudaStream_t stream) {
   const long long wanted = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
   const long long cap = (long long)sm_count * 8;   // 8 CTAs of 8 warps per SM: one wave, grid-stride beyond it
   const int blocks = (int)(wanted < cap ? wanted : cap);
   launch_after_predecessor(add_layernorm_kernel<T, VEC>, dim3(blocks), dim3(kWarpsPerBlock * 32), 0, stream,
                            (const uint4*)x, (const uint4*)residual, (const uint4*)gamma, (const uint4*)beta, (uint4*)out,
-                           rows, hidden, eps, row_mask, mask_elem);
+                           rows, hidden, eps, row_mask, mask_elem, (uint4*)out2, out2_rows);
 }
 
 template <typename T>
 int launch_typed(const void* x, const void* residual, const void* gamma, const void* beta, void* out, long long rows,
-                 int hidden, float eps, const void* row_mask, int mask_elem, int sm_count, cudaStream_t stream) {
+                 int hidden, float eps, const void* row_mask, int mask_elem, void* out2, const int32_t* out2_rows,
+                 int sm_count, cudaStream_t stream) {
   constexpr int E = Vec16<T>::kElems;
   const int vec = (hidden / E + 31) / 32;
 #define DFL_LN_CASE(V)                                                                              \
   if (vec <= V) {                                                                                   \
-    launch_one<T, V>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, sm_count, stream); \
+    launch_one<T, V>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, out2, out2_rows,   \
+                     sm_count, stream);                                                                        \
     return check_launch("add_layernorm_kernel");                                                    \
   }
   DFL_LN_CASE(1) DFL_LN_CASE(2) DFL_LN_CASE(3) DFL_LN_CASE(4) DFL_LN_CASE(6) DFL_LN_CASE(8) DFL_LN_CASE(12)
@@ -196,18 +206,48 @@ int launch_typed(const void* x, const void* residual, const void* gamma, const v
 
 }  // namespace
 
+namespace {
+// dst[r, :] = src[rows[r], :] (zeros for a negative entry); one warp per row, 16-byte vectors.
+__global__ void __launch_bounds__(256) copy_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                                        const int32_t* __restrict__ rows, long long n_rows,
+                                                        int vecs_per_row) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const long long stride = (long long)gridDim.x * 8;
+  wait_for_predecessor();
+  for (long long r = warp0; r < n_rows; r += stride) {
+    const long long from = rows[r];
+    for (int c = lane; c < vecs_per_row; c += 32)
+      dst[r * vecs_per_row + c] = from >= 0 ? src[from * vecs_per_row + c] : make_uint4(0, 0, 0, 0);
+  }
+}
+}  // namespace
+
+int launch_copy_rows(const void* src, void* dst, const int32_t* rows, long long n_rows, int row_bytes,
+                     cudaStream_t stream) {
+  static KernelDeviceConfig config;
+  int sm_count = 0;
+  if (int rc = configure_kernel(config, copy_rows_kernel, 0, &sm_count, "copy_rows_kernel")) return rc;
+  const long long wanted = (n_rows + 7) / 8, cap = (long long)sm_count * 8;
+  const int blocks = (int)(wanted < cap ? wanted : cap);
+  cudaError_t e = launch_after_predecessor(copy_rows_kernel, dim3(blocks), dim3(256), 0, stream, (const uint4*)src,
+                                           (uint4*)dst, rows, n_rows, row_bytes / 16);
+  if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "copy_rows_kernel: %s", cudaGetErrorString(e));
+  return check_launch("copy_rows_kernel");
+}
+
 int add_layernorm_max_hidden(size_t elem_size) { return 16 * 32 * (int)(16 / elem_size); }
 
 int launch_add_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* out,
                          long long rows, int hidden, float eps, int dtype, const void* row_mask, int mask_elem,
-                         cudaStream_t stream) {
+                         void* out2, const int32_t* out2_rows, cudaStream_t stream) {
   static KernelDeviceConfig config;   // only the SM count of the current device is needed (no shared memory)
   int sm_count = 0;
   if (int rc = configure_kernel(config, add_layernorm_kernel<float, 1>, 0, &sm_count, "add_layernorm_kernel")) return rc;
   switch (dtype) {
-    case DFL_F16: return launch_typed<__half>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, sm_count, stream);
-    case DFL_BF16: return launch_typed<__nv_bfloat16>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, sm_count, stream);
-    default: return launch_typed<float>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, sm_count, stream);
+    case DFL_F16: return launch_typed<__half>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, out2, out2_rows, sm_count, stream);
+    case DFL_BF16: return launch_typed<__nv_bfloat16>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, out2, out2_rows, sm_count, stream);
+    default: return launch_typed<float>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, out2, out2_rows, sm_count, stream);
   }
 }
 

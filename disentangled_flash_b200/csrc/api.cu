@@ -236,6 +236,14 @@ int dfl_conv1d(const DflConv1dParams* p, void* stream) {
   return launch_gemm_tc(g, (cudaStream_t)stream);
 }
 
+int dfl_copy_rows(const void* src, void* dst, const int32_t* rows_dev, int64_t n_rows, int32_t row_bytes, void* stream) {
+  if (n_rows < 0 || row_bytes < 16 || (row_bytes % 16)) return fail(DFL_ERR_BAD_ARG, "rows of a positive multiple of 16 bytes");
+  if (n_rows == 0) return DFL_OK;
+  if (!src || !dst || !rows_dev) return fail(DFL_ERR_BAD_ARG, "null pointer");
+  if (!aligned16(src) || !aligned16(dst)) return fail(DFL_ERR_ALIGNMENT, "pointers must be 16-byte aligned");
+  return launch_copy_rows(src, dst, rows_dev, n_rows, row_bytes, (cudaStream_t)stream);
+}
+
 int dfl_add_layernorm_supported(int dtype, int hidden) {
   if (!valid_dtype(dtype) || hidden < 1) return 0;
   const int elems = (int)(16 / dtype_size(dtype));
@@ -256,8 +264,10 @@ int dfl_add_layernorm(const DflAddLayerNormParams* p, void* stream) {
     return fail(DFL_ERR_ALIGNMENT, "pointers must be 16-byte aligned");
   if (p->row_mask && p->mask_elem_size != 1 && p->mask_elem_size != 4 && p->mask_elem_size != 8)
     return fail(DFL_ERR_BAD_ARG, "mask_elem_size must be 1, 4 or 8");
+  if ((p->out2 != nullptr) != (p->out2_rows != nullptr)) return fail(DFL_ERR_BAD_ARG, "out2 and out2_rows go together");
+  if (!aligned16(p->out2)) return fail(DFL_ERR_ALIGNMENT, "out2 must be 16-byte aligned");
   return launch_add_layernorm(p->x, p->residual, p->gamma, p->beta, p->out, p->rows, p->hidden, p->eps, p->dtype,
-                              p->row_mask, p->mask_elem_size, (cudaStream_t)stream);
+                              p->row_mask, p->mask_elem_size, p->out2, p->out2_rows, (cudaStream_t)stream);
 }
 
 int dfl_attention_rel_supported(const DflAttnRelParams* p) {
@@ -272,6 +282,8 @@ int dfl_attention_rel_fwd(const DflAttnRelParams* p, void* stream) {
   if (p->mask_elem_size != 1 && p->mask_elem_size != 4 && p->mask_elem_size != 8)
     return fail(DFL_ERR_BAD_ARG, "mask_elem_size must be 1, 4 or 8");
   if (!(p->scale > 0.0f)) return fail(DFL_ERR_BAD_ARG, "scale must be positive");
+  if ((p->out_row_base != nullptr) != (p->out_row_count != nullptr))
+    return fail(DFL_ERR_BAD_ARG, "out_row_base and out_row_count go together");
   if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out) ||
       (p->rel_key && !aligned16(p->rel_key)) || (p->rel_query && !aligned16(p->rel_query)))
     return fail(DFL_ERR_ALIGNMENT, "attention tensor not 16-byte aligned");

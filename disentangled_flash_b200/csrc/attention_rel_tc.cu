@@ -420,7 +420,12 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       const int bh = sl->bh, b = bh / H, h = bh - b * H;
       const int i0 = sl->i0;
 
-      if (!any_kept) {
+      // where the item's rows go: [B,L,H*d], or packed rows of the sequence (see DflAttnRelParams.out_row_base)
+      const long long out_row0 = p.out_row_base ? (long long)p.out_row_base[b] : (long long)b * L;
+      const int out_rows = p.out_row_base ? p.out_row_count[b] : L;
+      if (!any_kept && out_rows <= i0) {
+        // a tile of padded positions that the packed output does not hold: nothing to compute, nothing to store
+      } else if (!any_kept) {
         // Every query row of this tile is padding: each attends uniformly to all L keys, so every output row is
         // the column mean of V.  No score, no softmax: one pass over V by the 256 softmax threads.
         // 16-byte loads, every thread sums 8 columns over a stride of rows; the row groups of a warp are folded with
@@ -464,10 +469,10 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         ok = wwait(&bars->xbar, c_xb & 1u, 35);
         ++c_xb;
         if (!ok) break;
-        const int rows = L - i0 < BM ? L - i0 : BM;
+        const int rows = out_rows - i0 < BM ? out_rows - i0 : BM;
         constexpr int kVec = D / 8;  // 16-byte chunks per output row
         const uint4 mine = *reinterpret_cast<const uint4*>(mean + (tid % kVec) * 8);
-        T* out = reinterpret_cast<T*>(p.out) + ((long long)b * L + i0) * ((long long)H * D) + (long long)h * D;
+        T* out = reinterpret_cast<T*>(p.out) + (out_row0 + i0) * ((long long)H * D) + (long long)h * D;
         for (int e = tid; e < rows * kVec; e += 256) {
           const int rr = e / kVec, v = e - rr * kVec;
           *reinterpret_cast<uint4*>(out + (long long)rr * H * D + v * 8) = mine;
@@ -669,8 +674,8 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&bars->o_free);
-        if (row_ok) {
-          T* out = reinterpret_cast<T*>(p.out) + ((long long)b * L + i) * ((long long)H * D) + (long long)h * D + hf * OW;
+        if (row_ok && i < out_rows) {
+          T* out = reinterpret_cast<T*>(p.out) + (out_row0 + i) * ((long long)H * D) + (long long)h * D + hf * OW;
 #pragma unroll
           for (int v = 0; v < OW / 8; ++v) {
             uint4 pk;

@@ -199,7 +199,9 @@ int launch_attention_rel(const DflAttnRelParams& p, cudaStream_t stream);
 int add_layernorm_max_hidden(size_t elem_size);
 int launch_add_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* out,
                          long long rows, int hidden, float eps, int dtype, const void* row_mask, int mask_elem,
-                         cudaStream_t stream);
+                         void* out2, const int32_t* out2_rows, cudaStream_t stream);
+int launch_copy_rows(const void* src, void* dst, const int32_t* rows, long long n_rows, int row_bytes,
+                     cudaStream_t stream);
 int launch_selftest_bounded_wait(int* status, uint32_t limit_us, cudaStream_t stream);
 int launch_expand_rel_tables(const void* pos, const int32_t* lut, void* rel, int heads, int n_active, int seq_len,
                              int head_dim, int dtype, cudaStream_t stream);

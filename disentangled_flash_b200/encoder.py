@@ -467,6 +467,69 @@ class DebertaV2InferenceEncoder(nn.Module):
             return BaseModelOutput(last_hidden_state=state, hidden_states=collected, attentions=None)
         return (state,) if collected is None else (state, collected)
 
+    def forward_packed(self, hidden_states: torch.Tensor, attention_mask: torch.Tensor,
+                       lengths: Iterable[int]) -> BaseModelOutput:
+        """Forward of a right-padded batch without the padding: between the attention kernels the layers run on the
+        valid positions only, packed into consecutive rows (each sequence rounded up to 32 rows).
+
+        ``lengths`` are the valid lengths on the host (what a tokenizer returns); ``attention_mask`` must be the
+        matching prefix mask.  The result equals ``forward`` at the valid positions; padded positions of
+        ``last_hidden_state`` are unspecified (zero beyond each sequence's 32-row block), where the reference carries
+        values through every layer - the reason this is a method of its own and not the default.  Needs every layer's
+        blocks fused (a 16-bit Hugging Face shaped encoder on the single-launch attention path)."""
+
+        plans = self._validate_forward(hidden_states, attention_mask, False, None, None)
+        if not (all(a and b for a, b in self._fused_output_blocks) and all(self._fused_intermediates)):
+            raise NotImplementedError("forward_packed needs the fused output and intermediate blocks in every layer")
+        batch, length, hidden = hidden_states.shape
+        valid = [int(n) for n in lengths]
+        if len(valid) != batch or min(valid) < 0 or max(valid) > length:
+            raise ValueError("lengths must hold one length in [0, L] per sequence")
+        counts = [min(length, -(-n // 32) * 32) for n in valid]
+        bases = [0] * batch
+        for b in range(1, batch):
+            bases[b] = bases[b - 1] + counts[b - 1]
+        total = bases[-1] + counts[-1]
+        if total == 0:
+            raise ValueError("forward_packed needs at least one valid position")
+        device = hidden_states.device
+        source_rows = torch.cat([torch.arange(b * length, b * length + counts[b], dtype=torch.int32)
+                                 for b in range(batch)])
+        pack_rows = source_rows.to(device, non_blocking=True)
+        row_base = torch.tensor(bases, dtype=torch.int32).to(device, non_blocking=True)
+        row_count = torch.tensor(counts, dtype=torch.int32).to(device, non_blocking=True)
+        packed = (row_base, row_count, total)
+
+        keep = attention_mask.bool() if attention_mask.dtype.is_floating_point else attention_mask
+        state_u = hidden_states.contiguous()
+        state_p = _cabi.copy_rows(state_u.view(batch * length, hidden), pack_rows)
+        unpacked = [torch.zeros(batch * length, hidden, dtype=hidden_states.dtype, device=device) for _ in range(2)]
+        for depth, layer in enumerate(self.layer):
+            context = layer.attention.self.forward_packed_rows(state_u, keep, plans[depth], packed)
+            block = layer.attention.output
+            projected = F.linear(context, block.dense.weight, block.dense.bias)
+            mixed = _cabi.add_layernorm(projected, state_p, block.LayerNorm.weight, block.LayerNorm.bias,
+                                        float(block.LayerNorm.eps), out=projected)
+            dense = layer.intermediate.dense
+            inner = _cabi.dense(mixed, dense.weight, dense.bias, activation=_cabi.ACT_GELU, status=self._status_word)
+            block = layer.output
+            projected = F.linear(inner, block.dense.weight, block.dense.bias)
+            target = unpacked[depth % 2]
+            state_p = _cabi.add_layernorm(projected, mixed, block.LayerNorm.weight, block.LayerNorm.bias,
+                                          float(block.LayerNorm.eps), out=projected, scatter=(target, pack_rows))
+            state_u = target.view(batch, length, hidden)
+            if depth == 0 and self.conv is not None:
+                # the convolution runs along the sequence: on the unpacked layout, once per forward
+                if self._conv_fused.get(length, False):
+                    norm = self.conv.LayerNorm
+                    state_u = _conv_branch_op(hidden_states, state_u, attention_mask, self._conv_weight,
+                                              self.conv.conv.bias, norm.weight, norm.bias, float(norm.eps),
+                                              self._conv_activation_code, self._status_word)
+                else:
+                    state_u = self.conv(hidden_states, state_u, attention_mask).contiguous()
+                state_p = _cabi.copy_rows(state_u.view(batch * length, hidden), pack_rows)
+        return BaseModelOutput(last_hidden_state=state_u, hidden_states=None, attentions=None)
+
     def forward(self, hidden_states: torch.Tensor, attention_mask: torch.Tensor, output_hidden_states: bool = True,
                 output_attentions: bool = False, query_states: torch.Tensor | None = None,
                 relative_pos: torch.Tensor | None = None, return_dict: bool = True) -> Any:

@@ -249,6 +249,12 @@ typedef struct DflAttnRelParams {
   int32_t mask_elem_size; /* 1, 4 or 8 */
   float   scale;
   int32_t dtype, algo;
+  /* Packed output (both NULL: out is [B,L,H*d]).  With both given, out is [T,H*d]: the rows of sequence b start at
+   * row out_row_base[b] and only its first out_row_count[b] positions are written (query positions beyond that,
+   * padding, are not computed where a whole tile of them can be skipped and never stored).  No counterpart in the
+   * reference, which keeps padded positions in every tensor. */
+  const int32_t* out_row_base;   /* device [B] or NULL */
+  const int32_t* out_row_count;  /* device [B] or NULL */
 } DflAttnRelParams;
 DFL_API int dfl_expand_rel_tables(const void* pos, const int32_t* lut_dev, void* rel, int heads, int n_active,
                                   int seq_len, int head_dim, int dtype, void* stream);
@@ -330,8 +336,16 @@ typedef struct DflAddLayerNormParams {
   int32_t dtype;
   const void* row_mask;    /* [rows] or NULL: output rows whose element is zero are written as zeros */
   int32_t mask_elem_size;  /* 1, 4 or 8 */
+  void*       out2;        /* optional second copy of the result, row r written to row out2_rows[r] of out2 */
+  const int32_t* out2_rows; /* device [rows], required with out2; a negative entry skips the row */
 } DflAddLayerNormParams;
 DFL_API int dfl_add_layernorm_supported(int dtype, int hidden);
+/*
+ * Row gather: dst[r, :] = src[rows[r], :] for r < n_rows (rows of row_bytes bytes, a multiple of 16; a negative
+ * entry writes zeros).  Used to pack the valid positions of a padded batch into consecutive rows and back.
+ */
+DFL_API int dfl_copy_rows(const void* src, void* dst, const int32_t* rows_dev, int64_t n_rows, int32_t row_bytes,
+                          void* stream);
 DFL_API int dfl_add_layernorm(const DflAddLayerNormParams* p, void* stream);
 
 #ifdef __cplusplus
