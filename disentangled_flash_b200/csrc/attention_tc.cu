@@ -39,6 +39,7 @@ using attn::BN;  // 64 keys per tile
 using attn::Pack2;
 constexpr int kThreads = 256;
 constexpr int KV_STAGES = 2;
+constexpr int kMaxSmem = 232448;  // 227 KB opt-in limit per block
 constexpr int C_CHUNKS = 9;      // 16-byte chunks per staged c2p row: (BN-1+7)/8 + 1
 constexpr int P_CHUNKS = 25;     // 16-byte chunks per staged p2c row: (BM+BN-2+7)/8 + 1
 constexpr int C_PITCH = C_CHUNKS * 16;   // bytes
@@ -51,7 +52,9 @@ constexpr int COL_S = 0;             // two S buffers of BN fp32 columns
 constexpr int COL_P = 2 * BN;        // two P buffers of BN/2 columns (packed 16-bit pairs)
 constexpr int COL_O = 2 * BN + BN;   // D fp32 columns
 
-template <int D>
+// NB = relative-score stages: 2 when the shared memory of the sequence length leaves room (the stagers then fill
+// the next tile's windows while the softmax warps gather from the current one), else 1.
+template <int D, int NB_>
 struct Layout {
   static constexpr int kRowBytes = D >= 64 ? 128 : D * 2;      // swizzle span = bytes of one smem row
   static constexpr int kSub = D * 2 / kRowBytes;               // 64-column sub-tiles per row (2 for d=128)
@@ -61,7 +64,7 @@ struct Layout {
   static constexpr int kKV = 2 * kSub * kKSub;                  // K then V
   static constexpr int kBias = BM * C_PITCH + BN * P_PITCH;    // one relative-score stage
   static constexpr int kTmemCols = (COL_O + D) <= 256 ? 256 : 512;
-  static constexpr int kBiasStages = 1;                         // relative-score stages (shared memory leaves room for one)
+  static constexpr int kBiasStages = NB_;
   static constexpr int offQ = 0;
   static constexpr int offKV = offQ + kQ;
   static constexpr int offBias = offKV + KV_STAGES * kKV;
@@ -99,10 +102,9 @@ struct RoleCtx {
 
 // Softmax role: executed by warps 0-3, thread (warp*32+lane) owns query row i0 + warp*32 + lane,
 // which is TMEM lane warp*32+lane of every accumulator.
-template <typename T, int D>
+template <typename T, int D, int NB>
 __device__ __forceinline__ void softmax_role(const RoleCtx& c, const DflAttnParams& p, int warp, int lane) {
-  using LO = Layout<D>;
-  constexpr int NB = LO::kBiasStages;
+  using LO = Layout<D, NB>;
   Barriers* bars = c.bars;
   volatile int* abort_flag = &bars->abort_flag;
   const int L = c.L;
@@ -173,12 +175,11 @@ __device__ __forceinline__ void softmax_role(const RoleCtx& c, const DflAttnPara
   attn::softmax_store_row<T, D>(st, ok, row_ok, c.n_kt, t_o, out, &bars->o_ready, abort_flag, c.status_word);
 }
 
-template <typename T, int D>
+template <typename T, int D, int NB>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const DflAttnParams p, int* status_word) {
-  using LO = Layout<D>;
-  constexpr int NB = LO::kBiasStages;
+  using LO = Layout<D, NB>;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   Barriers* bars = reinterpret_cast<Barriers*>(smem + LO::offBar);
@@ -357,7 +358,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
   } else {
     RoleCtx ctx{smem, bars, lut_s, kbits, tmem_base, status_word, L, H, b, h, i0, n_kt, has_c2p, has_p2c};
-    softmax_role<T, D>(ctx, p, warp, lane);
+    softmax_role<T, D, NB>(ctx, p, warp, lane);
   }
 
   ptx::tc_fence_before();
@@ -369,9 +370,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
 namespace {
 
-template <typename T, int D>
+template <typename T, int D, int NB>
 int launch_typed(const DflAttnParams& p, cudaStream_t stream) {
-  using LO = Layout<D>;
+  using LO = Layout<D, NB>;
   const int L = p.seq_len;
   const int BH = p.batch * p.heads;
   const uint64_t row = (uint64_t)D * sizeof(T), seq = (uint64_t)L * row;
@@ -384,14 +385,13 @@ int launch_typed(const DflAttnParams& p, cudaStream_t stream) {
 
   // Shared memory: what the kernel uses, but never so little that more CTAs could become
   // resident on one SM than the 512 TMEM columns can serve (each CTA allocates kTmemCols).
-  constexpr int kMaxSmem = 232448;  // 227 KB opt-in limit per block
   constexpr int kMaxCtas = 512 / LO::kTmemCols;
   int smem = LO::total(L);
   const int floor_for_tmem = kMaxSmem / (kMaxCtas + 1) + 1024;
   if (smem < floor_for_tmem) smem = floor_for_tmem;
   if (smem > kMaxSmem) return fail(DFL_ERR_TOO_LARGE, "seq_len %d needs %d bytes of shared memory", L, smem);
 
-  auto kernel = attention_tc_kernel<T, D>;
+  auto kernel = attention_tc_kernel<T, D, NB>;
   static KernelDeviceConfig config;   // per instantiation
   rc = configure_kernel(config, kernel, smem, nullptr, "attention_tc_kernel");
   if (rc != DFL_OK) return rc;
@@ -406,12 +406,19 @@ int launch_typed(const DflAttnParams& p, cudaStream_t stream) {
   return check_launch("attention_tc_kernel");
 }
 
+template <typename T, int D>
+int launch_stages(const DflAttnParams& p, cudaStream_t stream) {
+  const bool has_pos = p.c2p != nullptr || p.p2c != nullptr;
+  if (has_pos && Layout<D, 2>::total(p.seq_len) <= kMaxSmem) return launch_typed<T, D, 2>(p, stream);
+  return launch_typed<T, D, 1>(p, stream);
+}
+
 template <typename T>
 int launch_d(const DflAttnParams& p, cudaStream_t stream) {
   switch (p.head_dim) {
-    case 32: return launch_typed<T, 32>(p, stream);
-    case 64: return launch_typed<T, 64>(p, stream);
-    case 128: return launch_typed<T, 128>(p, stream);
+    case 32: return launch_stages<T, 32>(p, stream);
+    case 64: return launch_stages<T, 64>(p, stream);
+    case 128: return launch_stages<T, 128>(p, stream);
   }
   return fail(DFL_ERR_UNSUPPORTED, "head_dim %d not in {32,64,128}", p.head_dim);
 }

@@ -102,7 +102,7 @@ struct GemmSmem {
 };
 
 // Epilogue of one accumulator chunk: 32 consecutive columns [n, n+32) of output row m, as fp32 bit patterns in r.
-// Adds the bias, rounds to T and stores 16 bytes at a time, head-major or row-major.
+// Adds the bias, rounds to T and stores 32 (or 16) bytes at a time, head-major or row-major.
 template <typename T>
 __device__ __forceinline__ void store_chunk(const GemmDesc& g, const uint32_t (&r)[32], int m, int n, int z, int ncols,
                                             int hd, const T* bias) {
@@ -118,6 +118,9 @@ __device__ __forceinline__ void store_chunk(const GemmDesc& g, const uint32_t (&
     dst = reinterpret_cast<T*>(g.out[0]) + (long long)z * g.stride_c + (long long)m * g.ldc + n;
     valid = ncols - n < 32 ? ncols - n : 32;  // multiple of 8
   }
+  // 32-byte stores (one full sector per thread and instruction) where the destination allows them
+  const bool wide = (reinterpret_cast<uintptr_t>(dst) & 31u) == 0;
+  uint4 held = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
   for (int v = 0; v < 4; ++v) {
     if (v * 8 >= valid) break;
@@ -138,7 +141,15 @@ __device__ __forceinline__ void store_chunk(const GemmDesc& g, const uint32_t (&
     T* ph = reinterpret_cast<T*>(&packed);
 #pragma unroll
     for (int j = 0; j < 8; ++j) ph[j] = Elem<T>::from_f(f[j]);
-    *reinterpret_cast<uint4*>(dst + v * 8) = packed;
+    const bool pair_end = (v & 1) != 0, pair_start_last = (v & 1) == 0 && (v + 1) * 8 >= valid;
+    if (wide && pair_end) {
+      asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst + (v - 1) * 8), "r"(held.x), "r"(held.y),
+                   "r"(held.z), "r"(held.w), "r"(packed.x), "r"(packed.y), "r"(packed.z), "r"(packed.w) : "memory");
+    } else if (wide && !pair_start_last) {
+      held = packed;
+    } else {
+      *reinterpret_cast<uint4*>(dst + v * 8) = packed;
+    }
   }
 }
 
@@ -154,7 +165,9 @@ __host__ __device__ inline bool tiled_store_ok(const GemmDesc& g) {
 // With `tiled` the rows go through the warp's staging buffers and leave as tiled bulk stores of full 128-byte
 // lines (per-thread stores would write every 32-byte sector in two halves from different instructions, and the
 // number of store requests, not the math, then bounds GEMMs with a short K).
-template <typename T>
+// CONV: the epilogue of the convolution branch (padding mask of the output row, tanh) is compiled in; plain GEMMs
+// take the instantiation without it (the extra code cost them 7 % when it was shared).
+template <typename T, bool CONV>
 __device__ __forceinline__ void drain_accumulator(const GemmDesc& g, const CUtensorMap* tmap_out, bool tiled,
                                                   unsigned char* buf, uint32_t taddr, int m_warp, int n0,
                                                   int col_begin, int z, bool ready, int lane) {
@@ -177,7 +190,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmDesc& g, const CUten
   }
   // padding mask of this thread's output row (convolution epilogue)
   bool keep_row = true;
-  if (g.row_mask && m_warp + lane < g.M) keep_row = mask_keep(g.row_mask, g.row_mask_elem, (long long)z * g.M + m_warp + lane);
+  if (CONV && g.row_mask && m_warp + lane < g.M) keep_row = mask_keep(g.row_mask, g.row_mask_elem, (long long)z * g.M + m_warp + lane);
 #pragma unroll 1
   for (int c0 = col_begin; c0 < col_begin + TN / 2; c0 += kStageCols) {
     const int n = n0 + c0;
@@ -201,14 +214,14 @@ __device__ __forceinline__ void drain_accumulator(const GemmDesc& g, const CUten
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] += Elem<T>::to_f(bh[j]);
       }
-      if (!keep_row) {
+      if (CONV && !keep_row) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = 0.0f;
       }
       if (g.activation == DFL_ACT_GELU) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = gelu_erf_fast(f[j]);
-      } else if (g.activation == DFL_ACT_TANH) {
+      } else if (CONV && g.activation == DFL_ACT_TANH) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = tanh_fast(f[j]);
       }
@@ -354,7 +367,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
       const int acc = lt & 1;
       if (ready) ready = ptx::mbar_wait(&tmem_full_bar[acc], (uint32_t)(lt >> 1) & 1u, abort_flag, g.status, 3);
       ptx::tc_fence_after();
-      drain_accumulator<T>(g, tmap_out.m, tiled != 0, staging,
+      drain_accumulator<T, false>(g, tmap_out.m, tiled != 0, staging,
                            tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * TN), m0 + quarter * 32, n0,
                            col_begin, z, ready, lane);
       // this warp has read its lanes of the accumulator: hand it back to the MMA issuer
@@ -386,7 +399,7 @@ constexpr int kPairSmem = kPairBarrierOffset + 512 + 1024;
 static_assert(kPairSmem <= kMaxSmem && GemmSmem<64>::kTotal <= kMaxSmem && GemmSmem<32>::kTotal <= kMaxSmem,
               "operand ring + output staging + barriers must fit the 227 KB a CTA can opt in to");
 
-template <typename T>
+template <typename T, bool CONV>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                     const __grid_constant__ OutMaps tmap_out, const GemmDesc g, const int num_kb, const int tiles_n,
@@ -452,8 +465,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         int m0, n0, z;
         tile_coords(tile, m0, n0, z);
         // k-steps: num_kb = taps x (k-blocks per tap); a plain GEMM has one tap with no row shift
-        const int taps = g.taps > 1 ? g.taps : 1;
-        const int kb_per_tap = num_kb / taps;
+        const int taps = CONV && g.taps > 1 ? g.taps : 1;
+        const int kb_per_tap = CONV ? num_kb / taps : num_kb;
+        const int w_batch = z % g.w_mod;
         int tap = 0, kb = 0;
         for (int step = 0; step < num_kb; ++step, ++it) {
           const int s = it % STAGES;
@@ -464,12 +478,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
           const uint32_t leader_full = ptx::map_to_cta(ptx::smem_u32(&full_bar[s]), 0);
           unsigned char* a = smem + s * kPairStageBytes;
           // rows above the first or below the last row of X_z are filled with zeros by the load
-          ptx::tma_load_3d_pair(a, &tmap_x, leader_full, kb * BK, m0 + (int)rank * TM + tap - (taps >> 1), z);
-          ptx::tma_load_3d_pair(a + kTileA, &tmap_w, leader_full, kb * BK, n0 + (int)rank * (TN / 2),
-                                taps > 1 ? tap : z % g.w_mod);
-          if (++kb == kb_per_tap) {
-            kb = 0;
-            ++tap;
+          if constexpr (CONV) {
+            ptx::tma_load_3d_pair(a, &tmap_x, leader_full, kb * BK, m0 + (int)rank * TM + tap - (taps >> 1), z);
+            ptx::tma_load_3d_pair(a + kTileA, &tmap_w, leader_full, kb * BK, n0 + (int)rank * (TN / 2),
+                                  taps > 1 ? tap : w_batch);
+            if (++kb == kb_per_tap) {
+              kb = 0;
+              ++tap;
+            }
+          } else {
+            ptx::tma_load_3d_pair(a, &tmap_x, leader_full, step * BK, m0 + (int)rank * TM, z);
+            ptx::tma_load_3d_pair(a + kTileA, &tmap_w, leader_full, step * BK, n0 + (int)rank * (TN / 2), w_batch);
           }
         }
       }
@@ -519,7 +538,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       const int acc = lt & 1;
       if (ready) ready = ptx::mbar_wait(&tmem_full_bar[acc], (uint32_t)(lt >> 1) & 1u, abort_flag, g.status, 13);
       ptx::tc_fence_after();
-      drain_accumulator<T>(g, tmap_out.m, tiled != 0, staging,
+      drain_accumulator<T, CONV>(g, tmap_out.m, tiled != 0, staging,
                            tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * TN),
                            m0 + (int)rank * TM + quarter * 32, n0, col_begin, z, ready, lane);
       ptx::tc_fence_before();
@@ -561,7 +580,7 @@ int encode_output_maps(const GemmDesc& g, OutMaps* maps, int* tiled) {
                               kStageCols, kStageRows, 128);
 }
 
-template <typename T>
+template <typename T, bool CONV>
 int launch_pair(const GemmDesc& g, cudaStream_t stream) {
   constexpr int BK = 64;
   const size_t es = sizeof(T);
@@ -580,7 +599,7 @@ int launch_pair(const GemmDesc& g, cudaStream_t stream) {
   rc = encode_output_maps<T>(g, &tmap_out, &tiled);
   if (rc != DFL_OK) return rc;
 
-  auto kernel = gemm_tc_pair_kernel<T>;
+  auto kernel = gemm_tc_pair_kernel<T, CONV>;
   static KernelDeviceConfig config;   // per template instantiation
   int num_sms = 0;
   rc = configure_kernel(config, kernel, kPairSmem, &num_sms, "gemm_tc_pair_kernel");
@@ -648,7 +667,10 @@ int launch_t(const GemmDesc& g, cudaStream_t stream) {
   if (!g.head_split && (g.ldc % 8)) return fail(DFL_ERR_ALIGNMENT, "ldc must be a multiple of 8");
   if (g.bias && !aligned16(g.bias)) return fail(DFL_ERR_ALIGNMENT, "bias not 16-byte aligned");
   // CTA pairs on 256 x 256 tiles when the problem has at least one full pair tile of rows and a 64-wide k-step
-  if (g.K >= 64 && g.M >= 2 * TM) return launch_pair<T>(g, stream);
+  if (g.K >= 64 && g.M >= 2 * TM) {
+    const bool conv = g.taps > 1 || g.row_mask || g.activation == DFL_ACT_TANH;
+    return conv ? launch_pair<T, true>(g, stream) : launch_pair<T, false>(g, stream);
+  }
   if (g.taps > 1 || g.row_mask) return fail(DFL_ERR_UNSUPPORTED, "taps and row masks need the pair kernel (M >= 256, K >= 64)");
   return g.K >= 64 ? launch_bk<T, 64>(g, stream) : launch_bk<T, 32>(g, stream);
 }
