@@ -60,6 +60,7 @@ class DflLinearParams(Structure):
         ("x", c_void_p), ("w", c_void_p), ("bias", c_void_p), ("out", c_void_p * 3),
         ("M", c_int32), ("K", c_int32), ("n_out", c_int32), ("heads", c_int32), ("head_dim", c_int32),
         ("rows_per_seq", c_int32), ("dtype", c_int32), ("algo", c_int32), ("status", c_void_p),
+        ("row_groups", c_void_p), ("out_seqs", c_int32),
     ]
 
 
@@ -271,8 +272,13 @@ def build_position_lut(seq_len: int, position_buckets: int, max_relative_positio
 
 def linear_heads(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, *, n_out: int, heads: int,
                  head_dim: int, rows_per_seq: int, algo: int = ALGO_AUTO,
-                 status: torch.Tensor | None = None) -> tuple[torch.Tensor, ...]:
-    """``x[M,K] @ weight[N,K]^T + bias`` written as ``n_out`` tensors ``[M/rows, heads, rows, head_dim]``."""
+                 status: torch.Tensor | None = None, row_groups: torch.Tensor | None = None,
+                 outs: tuple[torch.Tensor, ...] | None = None) -> tuple[torch.Tensor, ...]:
+    """``x[M,K] @ weight[N,K]^T + bias`` written as ``n_out`` tensors ``[M/rows, heads, rows, head_dim]``.
+
+    With ``row_groups`` (int32 ``[M/32]``) the rows of ``x`` are packed: group ``g`` of 32 rows goes to output rows
+    ``row_groups[g] .. +31`` of the caller's ``outs`` (``[B, heads, rows, head_dim]`` each), whose other rows stay
+    as they are."""
 
     lib = load_library()
     _require_cuda_contiguous("x", x)
@@ -281,9 +287,21 @@ def linear_heads(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | Non
     m, k = x2.shape
     if weight.shape != (n_out * heads * head_dim, k):
         raise ValueError(f"weight shape {tuple(weight.shape)} does not match [{n_out * heads * head_dim}, {k}]")
-    outs = tuple(torch.empty(m // rows_per_seq, heads, rows_per_seq, head_dim, dtype=x.dtype, device=x.device)
-                 for _ in range(n_out))
     p = DflLinearParams()
+    if row_groups is not None:
+        if outs is None or len(outs) != n_out:
+            raise ValueError("packed rows need the caller's output tensors")
+        if row_groups.dtype != torch.int32 or row_groups.numel() * 32 != m:
+            raise ValueError("row_groups must hold one int32 per 32 rows of x")
+        _require_cuda_contiguous("row_groups", row_groups)
+        for o in outs:
+            _require_cuda_contiguous("out", o)
+            if o.dtype != x.dtype or o.dim() != 4 or tuple(o.shape[1:]) != (heads, rows_per_seq, head_dim):
+                raise ValueError(f"output must be [B, {heads}, {rows_per_seq}, {head_dim}] of {x.dtype}")
+        p.row_groups, p.out_seqs = row_groups.data_ptr(), outs[0].shape[0]
+    else:
+        outs = tuple(torch.empty(m // rows_per_seq, heads, rows_per_seq, head_dim, dtype=x.dtype, device=x.device)
+                     for _ in range(n_out))
     p.x, p.w, p.bias = x2.data_ptr(), weight.data_ptr(), _ptr(bias)
     for i, o in enumerate(outs):
         p.out[i] = o.data_ptr()

@@ -415,15 +415,21 @@ class DisentangledFlashAttention(nn.Module):
 
     def forward_packed_rows(self, hidden_states: torch.Tensor, attention_mask: torch.Tensor,
                             plan: B200PreparedPositionPlan,
-                            packed_rows: tuple[torch.Tensor, torch.Tensor, int]) -> torch.Tensor:
+                            packed_rows: tuple[torch.Tensor, torch.Tensor, int],
+                            packed_input: tuple[torch.Tensor, tuple[torch.Tensor, ...]] | None = None) -> torch.Tensor:
         """``forward_prepared`` with the context written as packed rows ``[T, H*d]``: sequence ``b`` owns rows
         ``row_base[b] .. + row_count[b]`` (``packed_rows = (row_base, row_count, T)``); positions beyond
         ``row_count[b]`` are not stored.  Only on the single-launch attention path (FP16/BF16, head dim 32/64, a
-        relative term); no counterpart in the reference, which keeps padded positions in every tensor."""
+        relative term); no counterpart in the reference, which keeps padded positions in every tensor.
+
+        With ``packed_input = (row_groups, (q, k, v))`` the hidden states are packed rows ``[T, hid]`` as well
+        (``attention_mask`` still gives batch and length): the projection writes group ``g`` of 32 rows to rows
+        ``row_groups[g] .. +31`` of the caller's ``[B, H, L, d]`` buffers, whose remaining rows must hold finite
+        values (masked keys get probability zero, and zero times a stale NaN would still be NaN)."""
 
         self._validate_device_dtype(hidden_states)
         self._validate_inference_call()
-        batch_size, sequence_length = hidden_states.shape[:2]
+        batch_size, sequence_length = (attention_mask if packed_input is not None else hidden_states).shape[:2]
         if sequence_length != plan.sequence_length:
             raise ValueError(f"prepared length {plan.sequence_length} does not match input length {sequence_length}")
         if self._cached_qkv_weight is None:
@@ -434,10 +440,11 @@ class DisentangledFlashAttention(nn.Module):
             raise NotImplementedError("packed rows need the single-launch attention path (expanded position tables)")
         base_mask = _require_2d_padding_mask(attention_mask, batch_size, sequence_length)
         scale_factor = 1 + int("c2p" in self.pos_att_type) + int("p2c" in self.pos_att_type)
+        row_groups, buffers = packed_input if packed_input is not None else (None, None)
         query, key, value = _cabi.linear_heads(
             hidden_states.contiguous(), self._cached_qkv_weight, self._cached_qkv_bias, n_out=3,
             heads=self.num_attention_heads, head_dim=self.attention_head_size, rows_per_seq=sequence_length,
-            algo=self._algo, status=self._status_word)
+            algo=self._algo, status=self._status_word, row_groups=row_groups, outs=buffers)
         return _cabi.attention_rel_fwd(query, key, value, rel_key, rel_query, base_mask,
                                        1.0 / self._scale(scale_factor), status=self._status_word,
                                        packed_rows=packed_rows)

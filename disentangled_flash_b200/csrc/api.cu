@@ -89,7 +89,15 @@ int dfl_qkv_proj(const DflLinearParams* p, void* stream) {
     return fail(DFL_ERR_BAD_ARG, "non-positive size");
   if (!valid_head_dim(p->head_dim))
     return fail(DFL_ERR_UNSUPPORTED, "head_dim %d not in {32,64,128}", p->head_dim);
-  if (p->M % p->rows_per_seq) return fail(DFL_ERR_BAD_ARG, "M not a multiple of rows_per_seq");
+  if (p->row_groups) {
+    // packed rows: groups of 32 input rows with their destination rows; the kernels read one entry per 32 rows
+    if (p->M % 32 || p->rows_per_seq % 32) return fail(DFL_ERR_BAD_ARG, "row_groups need M and rows_per_seq in multiples of 32");
+    if (p->out_seqs < 1) return fail(DFL_ERR_BAD_ARG, "row_groups need out_seqs >= 1");
+    if (!use_tensor_cores(p->dtype, p->algo))
+      return fail(DFL_ERR_UNSUPPORTED, "row_groups are served by the tensor-core kernels only (FP16/BF16)");
+  } else if (p->M % p->rows_per_seq) {
+    return fail(DFL_ERR_BAD_ARG, "M not a multiple of rows_per_seq");
+  }
   if (!p->x || !p->w) return fail(DFL_ERR_BAD_ARG, "null input pointer");
   if (!aligned16(p->x) || !aligned16(p->w)) return fail(DFL_ERR_ALIGNMENT, "x/w not 16-byte aligned");
   for (int o = 0; o < p->n_out; ++o) {
@@ -104,6 +112,7 @@ int dfl_qkv_proj(const DflLinearParams* p, void* stream) {
   g.head_split = 1; g.heads = p->heads; g.head_dim = p->head_dim; g.rows_per_seq = p->rows_per_seq;
   g.dtype = p->dtype;
   g.status = p->status;
+  g.row_groups = p->row_groups; g.out_seqs = p->out_seqs;
   if (use_tensor_cores(p->dtype, p->algo)) return launch_gemm_tc(g, (cudaStream_t)stream);
   return launch_gemm_simt(g, (cudaStream_t)stream);
 }

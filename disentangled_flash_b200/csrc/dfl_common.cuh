@@ -157,6 +157,10 @@ struct GemmDesc {
   int taps;             // 0 or 1: plain GEMM
   const void* row_mask; // [batch, M] or null: output rows whose element is zero are set to 0 before the activation
   int row_mask_elem;    // element size of row_mask: 1, 4 or 8 bytes
+  // Packed input rows (head-split epilogue of the tensor-core kernels only): rows 32g .. 32g+31 of X are written to
+  // rows row_groups[g] .. +31 of the [out_seqs * rows_per_seq] output row space.  Null: row m goes to row m.
+  const int* row_groups;
+  int out_seqs;         // sequences of the output tensors when row_groups is set (else M / rows_per_seq)
 };
 
 // tanh for the GEMM epilogues of 16-bit outputs: 1 - 2 / (1 + e^(2x)) with approximate exp2 and reciprocal

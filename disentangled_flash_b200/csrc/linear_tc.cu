@@ -111,7 +111,8 @@ __device__ __forceinline__ void store_chunk(const GemmDesc& g, const uint32_t (&
   if (g.head_split) {
     const int which = n / hd, rem = n - which * hd;
     const int h = rem / g.head_dim, dd = rem - h * g.head_dim;
-    const int b = m / g.rows_per_seq, l = m - b * g.rows_per_seq;
+    const int row = g.row_groups ? __ldg(g.row_groups + (m >> 5)) + (m & 31) : m;
+    const int b = row / g.rows_per_seq, l = row - b * g.rows_per_seq;
     T* out = reinterpret_cast<T*>(which == 0 ? g.out[0] : (which == 1 ? g.out[1] : g.out[2]));
     dst = out + (((long long)b * g.heads + h) * g.rows_per_seq + l) * g.head_dim + dd;
   } else {
@@ -237,7 +238,8 @@ __device__ __forceinline__ void drain_accumulator(const GemmDesc& g, const CUten
       if (g.head_split) {
         const int which = n / hd, rem = n - which * hd;
         const int h = rem / g.head_dim, dd = rem - h * g.head_dim;
-        const int b = m_warp / g.rows_per_seq, l = m_warp - b * g.rows_per_seq;
+        const int row = g.row_groups ? __ldg(g.row_groups + (m_warp >> 5)) : m_warp;   // a warp's 32 rows: one group
+        const int b = row / g.rows_per_seq, l = row - b * g.rows_per_seq;
         ptx::tma_store_3d(&tmap_out[which], buf, dd, l, b * g.heads + h);
       } else {
         ptx::tma_store_3d(&tmap_out[0], buf, n, m_warp, z);
@@ -566,7 +568,7 @@ int encode_output_maps(const GemmDesc& g, OutMaps* maps, int* tiled) {
   if (!*tiled) return DFL_OK;
   const size_t es = sizeof(T);
   if (g.head_split) {
-    const uint64_t seqs = (uint64_t)(g.M / g.rows_per_seq) * g.heads;
+    const uint64_t seqs = (uint64_t)(g.row_groups ? g.out_seqs : g.M / g.rows_per_seq) * g.heads;
     for (int o = 0; o < 3; ++o) {
       if (!g.out[o]) continue;
       int rc = encode_tensor_map_3d(&maps->m[o], g.out[o], g.head_dim, g.rows_per_seq, seqs, (uint64_t)g.head_dim * es,

@@ -293,6 +293,7 @@ class DebertaV2InferenceEncoder(nn.Module):
         self._fused_output_blocks: list[tuple[bool, bool]] = [(False, False)] * len(self.layer)
         self._fused_intermediates: list[bool] = [False] * len(self.layer)
         self._conv_fused: dict[int, bool] = {}       # per bucket length: the fused convolution branch covers it
+        self._packed_qkv: dict[Any, tuple[torch.Tensor, ...]] = {}   # head-major Q/K/V buffers of forward_packed
         self._conv_weight: torch.Tensor | None = None   # nn.Conv1d weight as [taps, out, in]
         self._conv_activation_code = 0
         self._status_word: torch.Tensor | None = None
@@ -336,6 +337,7 @@ class DebertaV2InferenceEncoder(nn.Module):
 
         self._buckets.reset()
         self._conv_fused, self._conv_weight = {}, None
+        self._packed_qkv = {}
         self.position_plan_cache.clear()
         for attention in self._attention_modules():
             attention.clear_inference_cache()
@@ -503,9 +505,32 @@ class DebertaV2InferenceEncoder(nn.Module):
         keep = attention_mask.bool() if attention_mask.dtype.is_floating_point else attention_mask
         state_u = hidden_states.contiguous()
         state_p = _cabi.copy_rows(state_u.view(batch * length, hidden), pack_rows)
-        unpacked = [torch.zeros(batch * length, hidden, dtype=hidden_states.dtype, device=device) for _ in range(2)]
+        # With a bucket length in multiples of 32 the QKV projection reads the packed rows too and writes each group
+        # of 32 rows to its place in head-major buffers that are kept from call to call (rows no call has written
+        # yet are zero, later ones hold finite leftovers: masked keys must not be NaN).  The unpacked state is then
+        # needed only by the layer-0 convolution and as the result.
+        project_packed = length % 32 == 0
+        packed_input = None
+        if project_packed:
+            group_rows = torch.cat([torch.arange(b * length, b * length + counts[b], 32, dtype=torch.int32)
+                                    for b in range(batch)]).to(device, non_blocking=True)
+            first = self.layer[0].attention.self
+            key = (batch, length, first.num_attention_heads, first.attention_head_size, hidden_states.dtype, device)
+            buffers = self._packed_qkv.get(key)
+            if buffers is None:
+                buffers = tuple(torch.zeros(batch, first.num_attention_heads, length, first.attention_head_size,
+                                            dtype=hidden_states.dtype, device=device) for _ in range(3))
+                self._packed_qkv = {key: buffers}      # one shape at a time: 3 x B x L x hidden elements
+            packed_input = (group_rows, buffers)
+        unpacked = [torch.zeros(batch * length, hidden, dtype=hidden_states.dtype, device=device)
+                    for _ in range(1 if project_packed else 2)]
+        last = len(self.layer) - 1
         for depth, layer in enumerate(self.layer):
-            context = layer.attention.self.forward_packed_rows(state_u, keep, plans[depth], packed)
+            if project_packed:
+                context = layer.attention.self.forward_packed_rows(state_p, keep, plans[depth], packed,
+                                                                   packed_input=packed_input)
+            else:
+                context = layer.attention.self.forward_packed_rows(state_u, keep, plans[depth], packed)
             block = layer.attention.output
             projected = F.linear(context, block.dense.weight, block.dense.bias)
             mixed = _cabi.add_layernorm(projected, state_p, block.LayerNorm.weight, block.LayerNorm.bias,
@@ -514,11 +539,15 @@ class DebertaV2InferenceEncoder(nn.Module):
             inner = _cabi.dense(mixed, dense.weight, dense.bias, activation=_cabi.ACT_GELU, status=self._status_word)
             block = layer.output
             projected = F.linear(inner, block.dense.weight, block.dense.bias)
-            target = unpacked[depth % 2]
+            convolve = depth == 0 and self.conv is not None
+            scatter = None
+            if not project_packed or convolve or depth == last:
+                target = unpacked[depth % len(unpacked)]
+                scatter = (target, pack_rows)
+                state_u = target.view(batch, length, hidden)
             state_p = _cabi.add_layernorm(projected, mixed, block.LayerNorm.weight, block.LayerNorm.bias,
-                                          float(block.LayerNorm.eps), out=projected, scatter=(target, pack_rows))
-            state_u = target.view(batch, length, hidden)
-            if depth == 0 and self.conv is not None:
+                                          float(block.LayerNorm.eps), out=projected, scatter=scatter)
+            if convolve:
                 # the convolution runs along the sequence: on the unpacked layout, once per forward
                 if self._conv_fused.get(length, False):
                     norm = self.conv.LayerNorm
@@ -527,7 +556,8 @@ class DebertaV2InferenceEncoder(nn.Module):
                                               self._conv_activation_code, self._status_word)
                 else:
                     state_u = self.conv(hidden_states, state_u, attention_mask).contiguous()
-                state_p = _cabi.copy_rows(state_u.view(batch * length, hidden), pack_rows)
+                if depth != last:
+                    state_p = _cabi.copy_rows(state_u.view(batch * length, hidden), pack_rows)
         return BaseModelOutput(last_hidden_state=state_u, hidden_states=None, attentions=None)
 
     def forward(self, hidden_states: torch.Tensor, attention_mask: torch.Tensor, output_hidden_states: bool = True,

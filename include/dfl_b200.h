@@ -111,6 +111,13 @@ typedef struct DflLinearParams {
   int32_t dtype;        /* DFL_F16 / DFL_BF16 / DFL_F32                        */
   int32_t algo;         /* DFL_ALGO_*                                          */
   int32_t* status;      /* optional device int32, see dfl_check_status()       */
+  /* Optional packed input rows (FP16/BF16 tensor-core kernels; no counterpart in the reference, which projects the
+   * padded positions too): X holds only the kept rows, in groups of 32; group g (rows 32g .. 32g+31) is written to
+   * rows row_groups[g] .. +31 of the output row space [out_seqs * rows_per_seq] (row = sequence * rows_per_seq +
+   * position).  M and rows_per_seq must be multiples of 32, every group must lie inside one sequence, and output
+   * rows no group covers are left as they are.  NULL: row m of X is output row m and out_seqs is ignored. */
+  const int32_t* row_groups;   /* device int32 [M / 32] or NULL */
+  int32_t out_seqs;
 } DflLinearParams;
 DFL_API int dfl_qkv_proj(const DflLinearParams* p, void* stream);
 

@@ -62,8 +62,40 @@ def test_attention_packed_output_rows(dtype):
         assert torch.equal(packed[bases[b]:bases[b] + counts[b]], full[b, :counts[b]]), b
 
 
+@pytest.mark.parametrize("heads,head_dim", ((3, 64), (6, 32), (2, 128)))
+def test_projection_of_packed_rows(heads, head_dim):
+    """dfl_qkv_proj with row groups: packed input rows land where the unpacked projection puts them (bitwise), and
+    rows no group covers keep what the caller's buffers held."""
+
+    from disentangled_flash_b200 import _cabi as c
+
+    gen = torch.Generator().manual_seed(21)
+    batch, length, hidden = 5, 256, 192
+    width = heads * head_dim
+    x = torch.randn(batch, length, hidden, generator=gen).mul_(0.5).to(torch.float16).to(dev)
+    w = torch.randn(3 * width, hidden, generator=gen).mul_(0.06).to(torch.float16).to(dev)
+    bias = torch.randn(3 * width, generator=gen).to(torch.float16).to(dev)
+    counts = [256, 96, 160, 32, 64]
+    rows = torch.cat([torch.arange(b * length, b * length + counts[b], dtype=torch.int32) for b in range(batch)]).to(dev)
+    groups = rows[::32].contiguous()
+    full = c.linear_heads(x, w, bias, n_out=3, heads=heads, head_dim=head_dim, rows_per_seq=length)
+    packed_x = c.copy_rows(x.view(batch * length, hidden), rows)
+    outs = tuple(torch.full((batch, heads, length, head_dim), 7.0, dtype=torch.float16, device=dev) for _ in range(3))
+    got = c.linear_heads(packed_x, w, bias, n_out=3, heads=heads, head_dim=head_dim, rows_per_seq=length,
+                         row_groups=groups, outs=outs)
+    torch.cuda.synchronize()
+    for o in range(3):
+        for b in range(batch):
+            assert torch.equal(got[o][b, :, :counts[b]], full[o][b, :, :counts[b]]), (o, b)
+            assert (got[o][b, :, counts[b]:] == 7.0).all(), (o, b)
+    with pytest.raises(c.DflError):   # strict FP32 has no packed projection
+        c.linear_heads(packed_x.float(), w.float(), bias.float(), n_out=3, heads=heads, head_dim=head_dim,
+                       rows_per_seq=length, row_groups=groups, outs=tuple(o.float() for o in outs))
+
+
+@pytest.mark.parametrize("length", (256, 250))   # 250: not a multiple of 32, the projection stays on unpacked rows
 @pytest.mark.parametrize("dtype_name", ("fp16", "bf16"))
-def test_forward_packed_matches_forward_at_valid_positions(dtype_name):
+def test_forward_packed_matches_forward_at_valid_positions(dtype_name, length):
     import hf_modules
     import disentangled_flash_b200 as df
     from oracle.encoder import oracle_encoder_forward
@@ -78,12 +110,12 @@ def test_forward_packed_matches_forward_at_valid_positions(dtype_name):
     backbone = hf_modules.Backbone(cfg, vocab_size=8).eval()
     backbone.load_state_dict(rounded)
     backbone = backbone.to(dev, dtype)
-    df.optimize_deberta(backbone, sequence_lengths=[256])
+    df.optimize_deberta(backbone, sequence_lengths=[length])
     encoder = backbone.encoder
-    lengths = [256, 97, 160, 1, 33]
+    lengths = [length, 97, 160, 1, 33]
     gen = torch.Generator().manual_seed(6)
-    hidden = torch.randn(5, 256, 128, generator=gen).mul_(0.5).to(dtype)
-    mask = torch.arange(256)[None, :] < torch.tensor(lengths)[:, None]
+    hidden = torch.randn(5, length, 128, generator=gen).mul_(0.5).to(dtype)
+    mask = torch.arange(length)[None, :] < torch.tensor(lengths)[:, None]
     hidden = hidden * mask[..., None]          # embeddings of padding are zero, as Hugging Face's embeddings give them
     with torch.inference_mode():
         want = encoder(hidden.to(dev), mask.to(dev)).last_hidden_state.float().cpu()
@@ -95,7 +127,7 @@ def test_forward_packed_matches_forward_at_valid_positions(dtype_name):
     assert err.max().item() <= 8 * ulps * max(1.0, want[mask].abs().max().item()), err.max().item()
     # beyond a sequence's 32-row block nothing is written
     for b, n in enumerate(lengths):
-        block_end = min(256, -(-n // 32) * 32)
+        block_end = min(length, -(-n // 32) * 32)
         assert not got[b, block_end:].any().item()
     reference.load_state_dict(rounded)
     oracle = oracle_encoder_forward(reference, cfg, hidden.float(), mask)
