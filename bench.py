@@ -630,7 +630,7 @@ def run_v3_base(args, ctx: GpuContext) -> None:
         kept = sum(min(seq_len, -(-n // 32) * 32) for n in host_lengths[0]) / float(args.batch * seq_len)
         packed = {"value": seqs / (ms_packed / 1e3), "unit": "sequences/s", "ms_per_step": ms_packed / args.steps,
                   "rows_kept": kept,
-                  "note": "forward_packed(): dense layers, GELU and layer norms on the valid positions only (each "
+                  "note": "forward_packed(): projections, dense layers, GELU and layer norms on the valid positions only (each "
                           "sequence rounded up to 32 rows); equal to the padded forward at valid positions"}
 
     del encoder, dev_batches, dev_hidden
