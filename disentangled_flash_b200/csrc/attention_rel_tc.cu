@@ -406,7 +406,10 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     float* xmax = reinterpret_cast<float*>(smem + LO::offXmax);
     float* xsum = reinterpret_cast<float*>(smem + LO::offXsum);
     uint64_t* pair2 = &bars->pair2[q4];
-    uint32_t c_s = 0, c_cr = 0, c_pt = 0, c_pv = 0, c_p2 = 0, c_xb = 0;
+    // Two running counts give every barrier phase of this role: c_t = key tiles started (all items), c_i = items with
+    // kept rows finished.  Per tile one phase each of s_full, c2p_ready, pt_ready and o_ready, per tile and per item
+    // one of pair2; an item of padded rows only uses xbar exactly twice (phases 0 and 1).
+    uint32_t c_t = 0, c_i = 0;
     bool ok = true;
 
     int k = 0;
@@ -455,8 +458,7 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&bars->xbar);
-        ok = wwait(&bars->xbar, c_xb & 1u, 34);
-        ++c_xb;
+        ok = wwait(&bars->xbar, 0u, 34);
         if (!ok) break;
         if (tid < D) {
           float total = 0.0f;
@@ -466,8 +468,7 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&bars->xbar);
-        ok = wwait(&bars->xbar, c_xb & 1u, 35);
-        ++c_xb;
+        ok = wwait(&bars->xbar, 1u, 35);
         if (!ok) break;
         const int rows = out_rows - i0 < BM ? out_rows - i0 : BM;
         constexpr int kVec = D / 8;  // 16-byte chunks per output row
@@ -490,16 +491,11 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           // ring column of (row r, key x of the tile): (128 * (u & 1) + 128 - r + x) mod 256
           const uint32_t cb = (128u * (uint32_t)(u & 1) + 128u - (uint32_t)r + 64u * (uint32_t)hf) & 255u;
 
-          ok = wwait(&bars->s_full, c_s & 1u, 41);
-          ++c_s;
-          if (ok && has_c2p) {
-            ok = wwait(&bars->c2p_ready, c_cr & 1u, 42);
-            ++c_cr;
-          }
-          if (ok && has_p2c) {
-            ok = wwait(&bars->pt_ready, c_pt & 1u, 44);
-            ++c_pt;
-          }
+          const uint32_t tile_phase = c_t & 1u;
+          ++c_t;
+          ok = wwait(&bars->s_full, tile_phase, 41);
+          if (ok && has_c2p) ok = wwait(&bars->c2p_ready, tile_phase, 42);
+          if (ok && has_p2c) ok = wwait(&bars->pt_ready, tile_phase, 44);
           if (!ok) break;
           ptx::tc_fence_after();
 
@@ -568,14 +564,14 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           if (lane == 0 && has_c2p) ptx::mbar_arrive(&bars->ring_release);
           const float my_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
           // the row maximum of the tile needs the other half of the keys: exchange through shared memory
-          float* xm = xmax + (c_p2 & 1u) * (2 * BM);
+          const uint32_t pair_phase = (c_t + c_i + 1u) & 1u;   // c_t - 1 tiles and c_i items before this exchange
+          float* xm = xmax + pair_phase * (2 * BM);
           xm[hf * BM + r] = my_max;
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(pair2);
           ptx::tmem_wait_st();
           DFL_TMEM_LD32_F(t_s, nxt, 0);   // first chunk of pass 2, in flight during the exchange
-          ok = wwait(pair2, c_p2 & 1u, 45);
-          ++c_p2;
+          ok = wwait(pair2, pair_phase, 45);
           if (!ok) break;
           const float tile_max = fmaxf(my_max, xm[(1 - hf) * BM + r]);
 
@@ -591,8 +587,7 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             m_run = m_new;
             l_run *= corr;
             if (u >= 1) {   // O holds the item's earlier tiles: rescale this thread's half of the columns
-              ok = wwait(&bars->o_ready, c_pv & 1u, 46);
-              ++c_pv;
+              ok = wwait(&bars->o_ready, c_t & 1u, 46);   // PV(u-1): c_t - 2 completed before it
               pv_seen = true;
               if (!ok) break;
               ptx::tc_fence_after();
@@ -639,8 +634,7 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             for (int x = 0; x < 16; ++x) add_pair<T>(sum[(2 * x) & 3], sum[(2 * x + 1) & 3], packed[x]);
             // the P buffer is the A operand of the previous tile's PV until that MMA completes
             if (q == 0 && u >= 1 && !pv_seen) {
-              ok = wwait(&bars->o_ready, c_pv & 1u, 47);
-              ++c_pv;
+              ok = wwait(&bars->o_ready, c_t & 1u, 47);
               if (!ok) break;
               ptx::tc_fence_after();
             }
@@ -656,15 +650,14 @@ attention_rel_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         if (!ok) break;
 
         // ---- the item's last PV, then normalise and store this thread's half of the output columns
-        ok = wwait(&bars->o_ready, c_pv & 1u, 48);
-        ++c_pv;
+        ok = wwait(&bars->o_ready, (c_t & 1u) ^ 1u, 48);   // the item's last PV: c_t - 1 completed before it
         if (!ok) break;
         ptx::tc_fence_after();
         xsum[hf * BM + r] = l_run;
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(pair2);
-        ok = wwait(pair2, c_p2 & 1u, 49);
-        ++c_p2;
+        ok = wwait(pair2, (c_t + c_i) & 1u, 49);
+        ++c_i;
         if (!ok) break;
         const float inv = 1.0f / (l_run + xsum[(1 - hf) * BM + r]);
         uint32_t o[OW];
