@@ -147,3 +147,43 @@ def test_captured_buckets_replay_the_eager_forward_bitwise():
     encoder.check_device_status()
     with pytest.raises(ValueError, match="captured for"):
         graphs[64](torch.zeros(2, 64, 128, dtype=torch.float16, device=dev), torch.ones(2, 64, dtype=torch.bool, device=dev))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
+def test_second_device_in_one_process_gets_its_own_kernel_configuration():
+    """The shared-memory opt-in and the SM count are per-device attributes: every kernel family, called on cuda:0 and
+    then on cuda:1 from one process (plain launches, no peer access), gives the same bits on both."""
+
+    c = _cabi()
+    case = make_core_case(2, 2, 256, 64, torch.float16, seed=81, mask="right")
+    case128 = make_core_case(1, 2, 130, 128, torch.float16, seed=82, mask="right")
+    gen = torch.Generator().manual_seed(83)
+    x = torch.randn(2, 256, 192, generator=gen).mul_(0.5).to(torch.float16)
+    w = torch.randn(3 * 2 * 64, 192, generator=gen).mul_(0.06).to(torch.float16)
+    bias = torch.randn(3 * 2 * 64, generator=gen).to(torch.float16)
+    results = []
+    for index in (0, 1):
+        device = torch.device("cuda", index)
+        to = lambda t: t.to(device)  # noqa: E731
+        status = c.new_status_word(device)
+        lut = to(case["lut"])
+        rel = c.attention_rel_fwd(to(case["q"]), to(case["k"]), to(case["v"]),
+                                  c.expand_rel_tables(to(case["pos_key"]), lut, 256),
+                                  c.expand_rel_tables(to(case["pos_query"]), lut, 256), to(case["mask"]), case["scale"],
+                                  status=status)
+        q, k = to(case128["q"]), to(case128["k"])
+        c2p, p2c, ld = c.pos_scores(q, k, to(case128["pos_key"]), to(case128["pos_query"]), status=status)
+        two_call = c.attention_fwd(q, k, to(case128["v"]), c2p, p2c, to(case128["lut"]), to(case128["mask"]),
+                                   case128["scale"], ld_slots=ld, status=status)
+        heads = c.linear_heads(to(x), to(w), to(bias), n_out=3, heads=2, head_dim=64, rows_per_seq=256, status=status)
+        dense = c.dense(to(x).view(512, 192), to(w), to(bias), activation=c.ACT_GELU, status=status)
+        normed = c.add_layernorm(dense, dense, torch.ones(384, dtype=torch.float16, device=device),
+                                 torch.zeros(384, dtype=torch.float16, device=device), 1e-7)
+        fp32 = c.linear_heads(to(x).float(), to(w).float(), to(bias).float(), n_out=3, heads=2, head_dim=64,
+                              rows_per_seq=256, status=status)
+        torch.cuda.synchronize(device)
+        c.check_status(status)
+        results.append([t.cpu() for t in (rel, two_call, *heads, dense, normed, *fp32)])
+    assert_close(results[0][0], oracle_core(case), torch.float16, "single-launch attention on cuda:0")
+    for first, second in zip(*results):
+        assert torch.equal(first, second)
