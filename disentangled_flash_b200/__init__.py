@@ -8,6 +8,7 @@ sm_100a CUDA kernels behind a C ABI (``include/dfl_b200.h``).
 
 from .attention import B200PreparedPositionPlan, DisentangledFlashAttention
 from .config import DebertaAttentionConfig
+from .embeddings import fuse_deberta_embeddings
 from .encoder import (
     DebertaV2InferenceEncoder,
     capture_deberta_buckets,
@@ -31,5 +32,6 @@ __all__ = [
     "compile_deberta_buckets",
     "enable_deberta_inference",
     "enable_deberta_v2_inference",
+    "fuse_deberta_embeddings",
     "optimize_deberta",
 ]

@@ -40,6 +40,7 @@ EXPORTED_SYMBOLS = (
     "dfl_qkv_proj",
     "dfl_gather_slots",
     "dfl_add_layernorm",
+    "dfl_embed_layernorm",
     "dfl_dense",
     "dfl_conv1d",
     "dfl_copy_rows",
@@ -124,6 +125,14 @@ class DflAddLayerNormParams(Structure):
                 ("row_mask", c_void_p), ("mask_elem_size", c_int), ("out2", c_void_p), ("out2_rows", c_void_p)]
 
 
+class DflEmbedLayerNormParams(Structure):
+    _fields_ = [("ids", c_void_p), ("table", c_void_p), ("pos_ids", c_void_p), ("pos_table", c_void_p),
+                ("gamma", c_void_p), ("beta", c_void_p), ("row_mask", c_void_p), ("out", c_void_p),
+                ("rows", ctypes.c_int64), ("vocab", ctypes.c_int64), ("positions", ctypes.c_int64),
+                ("hidden", c_int), ("eps", ctypes.c_float), ("dtype", c_int), ("id_elem_size", c_int),
+                ("mask_elem_size", c_int), ("status", c_void_p)]
+
+
 class DflError(RuntimeError):
     """A C entry point returned a negative status."""
 
@@ -170,6 +179,8 @@ def load_library() -> ctypes.CDLL:
     lib.dfl_add_layernorm_supported.argtypes = [c_int, c_int]
     lib.dfl_add_layernorm.restype = c_int
     lib.dfl_add_layernorm.argtypes = [POINTER(DflAddLayerNormParams), c_void_p]
+    lib.dfl_embed_layernorm.restype = c_int
+    lib.dfl_embed_layernorm.argtypes = [POINTER(DflEmbedLayerNormParams), c_void_p]
     lib.dfl_gather_slots.restype = c_int
     lib.dfl_gather_slots.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
     lib.dfl_pos_scores.restype = c_int
@@ -415,6 +426,45 @@ def copy_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor | None = 
     with torch.cuda.device(src.device):
         _check(lib.dfl_copy_rows(src.data_ptr(), out.data_ptr(), rows.data_ptr(), rows.numel(), row_bytes,
                                  _stream(src.device)), "dfl_copy_rows")
+    return out
+
+
+def embed_layernorm(ids: torch.Tensor, table: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
+                    eps: float, *, row_mask: torch.Tensor | None = None, pos_ids: torch.Tensor | None = None,
+                    pos_table: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+    """``LayerNorm(table[ids] (+ pos_table[pos_ids])) * weight + bias`` with the rows whose ``row_mask`` element is
+    zero written as zeros: ``ids`` of any shape (int32 or int64) -> ``ids.shape + [hidden]``.  An id outside its
+    table reads as zeros and is reported by ``check_status(status)``."""
+
+    lib = load_library()
+    hidden = table.shape[-1]
+    for name, t in (("ids", ids), ("table", table), ("weight", weight), ("bias", bias), ("row_mask", row_mask),
+                    ("pos_ids", pos_ids), ("pos_table", pos_table)):
+        if t is not None:
+            _require_cuda_contiguous(name, t)
+    if ids.dtype not in (torch.int32, torch.int64):
+        raise TypeError("ids must be int32 or int64")
+    for name, t in (("weight", weight), ("bias", bias), ("pos_table", pos_table)):
+        if t is not None and t.dtype != table.dtype:
+            raise TypeError(f"{name} must have the dtype of the table ({table.dtype}), got {t.dtype}")
+    if table.dim() != 2 or weight.numel() != hidden or (bias is not None and bias.numel() != hidden):
+        raise ValueError("table must be [vocab, hidden] and weight, bias [hidden]")
+    if (pos_ids is None) != (pos_table is None):
+        raise ValueError("pos_ids and pos_table go together")
+    if pos_ids is not None and (pos_ids.dtype != ids.dtype or pos_ids.shape != ids.shape or pos_table.shape[-1] != hidden):
+        raise ValueError("pos_ids must have the type and shape of ids, pos_table the width of table")
+    if row_mask is not None and row_mask.numel() != ids.numel():
+        raise ValueError("row_mask must have one element per id")
+    out = torch.empty(*ids.shape, hidden, dtype=table.dtype, device=table.device)
+    p = DflEmbedLayerNormParams()
+    p.ids, p.table, p.pos_ids, p.pos_table = _ptr(ids), _ptr(table), _ptr(pos_ids), _ptr(pos_table)
+    p.gamma, p.beta, p.row_mask, p.out = _ptr(weight), _ptr(bias), _ptr(row_mask), _ptr(out)
+    p.rows, p.vocab, p.positions = ids.numel(), table.shape[0], pos_table.shape[0] if pos_table is not None else 0
+    p.hidden, p.eps, p.dtype, p.id_elem_size = hidden, float(eps), dtype_code(table.dtype), ids.element_size()
+    p.mask_elem_size = row_mask.element_size() if row_mask is not None else 1
+    p.status = _ptr(status)
+    with torch.cuda.device(table.device):
+        _check(lib.dfl_embed_layernorm(ctypes.byref(p), _stream(table.device)), "dfl_embed_layernorm")
     return out
 
 

@@ -93,13 +93,28 @@ __device__ __forceinline__ uint4 ld_stream(const uint4* p) {
   return v;
 }
 
+// Row gather for the embedding front-end: where the rows of x (and of residual) come from.
+struct RowSource {
+  const void* x_rows;        // [rows] indices into x (token ids), or null: row r of x is row r
+  const void* res_rows;      // [rows] indices into residual (position ids), or null
+  int idx_elem;              // 4 or 8: int32 / int64 indices
+  long long x_limit;         // rows of the x table
+  long long res_limit;       // rows of the residual table
+  int* status;               // device word that receives kStatusBadIndex when an index is out of range
+};
+constexpr int kStatusBadIndex = 98;
+
+__device__ __forceinline__ long long load_index(const void* idx, int elem, long long i) {
+  return elem == 8 ? reinterpret_cast<const long long*>(idx)[i] : (long long)reinterpret_cast<const int*>(idx)[i];
+}
+
 // Vector j of lane l covers columns (j*32 + l) * E .. +E: a warp reads 512 contiguous bytes per vector index.
 template <typename T, int VEC>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 add_layernorm_kernel(const uint4* x, const uint4* residual, const uint4* __restrict__ gamma,
                      const uint4* __restrict__ beta, uint4* out, long long rows, int hidden, float eps,
                      const void* __restrict__ row_mask, int mask_elem, uint4* out2,
-                     const int32_t* __restrict__ out2_rows) {
+                     const int32_t* __restrict__ out2_rows, const RowSource src) {
   constexpr int E = Vec16<T>::kElems;
   const int lane = threadIdx.x & 31;
   const int vecs_per_row = hidden / E;
@@ -108,15 +123,29 @@ add_layernorm_kernel(const uint4* x, const uint4* residual, const uint4* __restr
   const long long stride = (long long)gridDim.x * kWarpsPerBlock;
   wait_for_predecessor();
   for (long long row = warp0; row < rows; row += stride) {
-    const uint4* xr = x + row * vecs_per_row;
-    const uint4* rr = residual ? residual + row * vecs_per_row : nullptr;
+    // an index outside its table reads as a row of zeros and is reported through the status word
+    long long x_row = row, res_row = row;
+    if (src.x_rows) {
+      x_row = load_index(src.x_rows, src.idx_elem, row);
+      if (x_row < 0 || x_row >= src.x_limit) x_row = -1;
+    }
+    if (src.res_rows) {
+      res_row = load_index(src.res_rows, src.idx_elem, row);
+      if (res_row < 0 || res_row >= src.res_limit) res_row = -1;
+    }
+    if ((x_row < 0 || res_row < 0) && src.status && lane == 0) atomicCAS(src.status, 0, kStatusBadIndex);
+    const uint4* xr = x + x_row * vecs_per_row;
+    const uint4* rr = residual ? residual + res_row * vecs_per_row : nullptr;
     uint4 rx[VEC], rres[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) {
       const int c = j * 32 + lane;
-      rx[j] = c < vecs_per_row ? ld_stream(xr + c) : make_uint4(0, 0, 0, 0);
+      rx[j] = c < vecs_per_row && x_row >= 0 ? ld_stream(xr + c) : make_uint4(0, 0, 0, 0);
     }
-    if (rr) {
+    if (rr && res_row < 0) {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) rres[j] = make_uint4(0, 0, 0, 0);
+    } else if (rr) {
 #pragma unroll
       for (int j = 0; j < VEC; ++j) {
         const int c = j * 32 + lane;
@@ -177,25 +206,25 @@ add_layernorm_kernel(const uint4* x, const uint4* residual, const uint4* __restr
 template <typename T, int VEC>
 void launch_one(const void* x, const void* residual, const void* gamma, const void* beta, void* out, long long rows,
                 int hidden, float eps, const void* row_mask, int mask_elem, void* out2, const int32_t* out2_rows,
-                int sm_count, cudaStream_t stream) {
+                const RowSource& src, int sm_count, cudaStream_t stream) {
   const long long wanted = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
   const long long cap = (long long)sm_count * 8;   // 8 CTAs of 8 warps per SM: one wave, grid-stride beyond it
   const int blocks = (int)(wanted < cap ? wanted : cap);
   launch_after_predecessor(add_layernorm_kernel<T, VEC>, dim3(blocks), dim3(kWarpsPerBlock * 32), 0, stream,
                            (const uint4*)x, (const uint4*)residual, (const uint4*)gamma, (const uint4*)beta, (uint4*)out,
-                           rows, hidden, eps, row_mask, mask_elem, (uint4*)out2, out2_rows);
+                           rows, hidden, eps, row_mask, mask_elem, (uint4*)out2, out2_rows, src);
 }
 
 template <typename T>
 int launch_typed(const void* x, const void* residual, const void* gamma, const void* beta, void* out, long long rows,
                  int hidden, float eps, const void* row_mask, int mask_elem, void* out2, const int32_t* out2_rows,
-                 int sm_count, cudaStream_t stream) {
+                 const RowSource& src, int sm_count, cudaStream_t stream) {
   constexpr int E = Vec16<T>::kElems;
   const int vec = (hidden / E + 31) / 32;
 #define DFL_LN_CASE(V)                                                                              \
   if (vec <= V) {                                                                                   \
     launch_one<T, V>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, out2, out2_rows,   \
-                     sm_count, stream);                                                                        \
+                     src, sm_count, stream);                                                                   \
     return check_launch("add_layernorm_kernel");                                                    \
   }
   DFL_LN_CASE(1) DFL_LN_CASE(2) DFL_LN_CASE(3) DFL_LN_CASE(4) DFL_LN_CASE(6) DFL_LN_CASE(8) DFL_LN_CASE(12)
@@ -238,17 +267,37 @@ int launch_copy_rows(const void* src, void* dst, const int32_t* rows, long long 
 
 int add_layernorm_max_hidden(size_t elem_size) { return 16 * 32 * (int)(16 / elem_size); }
 
-int launch_add_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* out,
-                         long long rows, int hidden, float eps, int dtype, const void* row_mask, int mask_elem,
-                         void* out2, const int32_t* out2_rows, cudaStream_t stream) {
+namespace {
+int launch_rows(const void* x, const void* residual, const void* gamma, const void* beta, void* out, long long rows,
+                int hidden, float eps, int dtype, const void* row_mask, int mask_elem, void* out2,
+                const int32_t* out2_rows, const RowSource& src, cudaStream_t stream) {
   static KernelDeviceConfig config;   // only the SM count of the current device is needed (no shared memory)
   int sm_count = 0;
   if (int rc = configure_kernel(config, add_layernorm_kernel<float, 1>, 0, &sm_count, "add_layernorm_kernel")) return rc;
   switch (dtype) {
-    case DFL_F16: return launch_typed<__half>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, out2, out2_rows, sm_count, stream);
-    case DFL_BF16: return launch_typed<__nv_bfloat16>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, out2, out2_rows, sm_count, stream);
-    default: return launch_typed<float>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, out2, out2_rows, sm_count, stream);
+    case DFL_F16: return launch_typed<__half>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, out2, out2_rows, src, sm_count, stream);
+    case DFL_BF16: return launch_typed<__nv_bfloat16>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, out2, out2_rows, src, sm_count, stream);
+    default: return launch_typed<float>(x, residual, gamma, beta, out, rows, hidden, eps, row_mask, mask_elem, out2, out2_rows, src, sm_count, stream);
   }
+}
+}  // namespace
+
+int launch_add_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* out,
+                         long long rows, int hidden, float eps, int dtype, const void* row_mask, int mask_elem,
+                         void* out2, const int32_t* out2_rows, cudaStream_t stream) {
+  const RowSource plain{nullptr, nullptr, 4, 0, 0, nullptr};
+  return launch_rows(x, residual, gamma, beta, out, rows, hidden, eps, dtype, row_mask, mask_elem, out2, out2_rows, plain,
+                     stream);
+}
+
+// Embedding front-end: out[r] = LayerNorm(table[ids[r]] (+ pos_table[pos_ids[r]])), masked rows zero.
+int launch_embed_layernorm(const void* ids, const void* table, long long vocab, const void* pos_ids,
+                           const void* pos_table, long long positions, int idx_elem, const void* gamma,
+                           const void* beta, void* out, long long rows, int hidden, float eps, int dtype,
+                           const void* row_mask, int mask_elem, int* status, cudaStream_t stream) {
+  const RowSource src{ids, pos_table ? pos_ids : nullptr, idx_elem, vocab, positions, status};
+  return launch_rows(table, pos_table, gamma, beta, out, rows, hidden, eps, dtype, row_mask, mask_elem, nullptr, nullptr,
+                     src, stream);
 }
 
 }  // namespace dfl

@@ -42,6 +42,8 @@ int dfl_check_status(int32_t* status_dev, void* stream) {
   e = cudaMemsetAsync(status_dev, 0, sizeof(code), s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   if (e != cudaSuccess) return fail(DFL_ERR_LAUNCH, "clearing the status word: %s", cudaGetErrorString(e));
+  if (code == 98)   // dfl_embed_layernorm: the one code that is not a wait
+    return fail(DFL_ERR_BAD_ARG, "an embedding index was outside its table (that row was read as zeros)");
   return fail(DFL_ERR_DEVICE_TIMEOUT, "a bounded device-side wait expired (wait code %d); outputs since the last check are invalid",
               (int)code);
 }
@@ -277,6 +279,28 @@ int dfl_add_layernorm(const DflAddLayerNormParams* p, void* stream) {
   if (!aligned16(p->out2)) return fail(DFL_ERR_ALIGNMENT, "out2 must be 16-byte aligned");
   return launch_add_layernorm(p->x, p->residual, p->gamma, p->beta, p->out, p->rows, p->hidden, p->eps, p->dtype,
                               p->row_mask, p->mask_elem_size, p->out2, p->out2_rows, (cudaStream_t)stream);
+}
+
+int dfl_embed_layernorm(const DflEmbedLayerNormParams* p, void* stream) {
+  if (!p) return fail(DFL_ERR_BAD_ARG, "null params");
+  if (!valid_dtype(p->dtype)) return fail(DFL_ERR_BAD_ARG, "unknown dtype %d", p->dtype);
+  if (p->rows < 0 || p->hidden < 1 || p->vocab < 1) return fail(DFL_ERR_BAD_ARG, "non-positive size");
+  if (!(p->eps >= 0.0f)) return fail(DFL_ERR_BAD_ARG, "eps must be non-negative");
+  if (!dfl_add_layernorm_supported(p->dtype, p->hidden))
+    return fail(DFL_ERR_UNSUPPORTED, "hidden size %d: rows must be multiples of 16 bytes and at most %d elements",
+                p->hidden, add_layernorm_max_hidden(dtype_size(p->dtype)));
+  if (p->rows == 0) return DFL_OK;
+  if (!p->ids || !p->table || !p->gamma || !p->out) return fail(DFL_ERR_BAD_ARG, "null pointer");
+  if (p->id_elem_size != 4 && p->id_elem_size != 8) return fail(DFL_ERR_BAD_ARG, "id_elem_size must be 4 or 8");
+  if ((p->pos_ids != nullptr) != (p->pos_table != nullptr)) return fail(DFL_ERR_BAD_ARG, "pos_ids and pos_table go together");
+  if (p->pos_table && p->positions < 1) return fail(DFL_ERR_BAD_ARG, "positions must be positive");
+  if (p->row_mask && p->mask_elem_size != 1 && p->mask_elem_size != 4 && p->mask_elem_size != 8)
+    return fail(DFL_ERR_BAD_ARG, "mask_elem_size must be 1, 4 or 8");
+  if (!aligned16(p->table) || !aligned16(p->pos_table) || !aligned16(p->gamma) || !aligned16(p->beta) || !aligned16(p->out))
+    return fail(DFL_ERR_ALIGNMENT, "pointers must be 16-byte aligned");
+  return launch_embed_layernorm(p->ids, p->table, p->vocab, p->pos_ids, p->pos_table, p->positions, p->id_elem_size,
+                                p->gamma, p->beta, p->out, p->rows, p->hidden, p->eps, p->dtype, p->row_mask,
+                                p->mask_elem_size, p->status, (cudaStream_t)stream);
 }
 
 int dfl_attention_rel_supported(const DflAttnRelParams* p) {

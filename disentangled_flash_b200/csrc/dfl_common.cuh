@@ -204,6 +204,10 @@ int add_layernorm_max_hidden(size_t elem_size);
 int launch_add_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* out,
                          long long rows, int hidden, float eps, int dtype, const void* row_mask, int mask_elem,
                          void* out2, const int32_t* out2_rows, cudaStream_t stream);
+int launch_embed_layernorm(const void* ids, const void* table, long long vocab, const void* pos_ids,
+                           const void* pos_table, long long positions, int idx_elem, const void* gamma,
+                           const void* beta, void* out, long long rows, int hidden, float eps, int dtype,
+                           const void* row_mask, int mask_elem, int* status, cudaStream_t stream);
 int launch_copy_rows(const void* src, void* dst, const int32_t* rows, long long n_rows, int row_bytes,
                      cudaStream_t stream);
 int launch_selftest_bounded_wait(int* status, uint32_t limit_us, cudaStream_t stream);

@@ -355,6 +355,36 @@ DFL_API int dfl_copy_rows(const void* src, void* dst, const int32_t* rows_dev, i
                           void* stream);
 DFL_API int dfl_add_layernorm(const DflAddLayerNormParams* p, void* stream);
 
+/*
+ * Embedding front-end in one pass: token-embedding gather, optional position-embedding add, LayerNorm, padding mask:
+ *     out[r, :] = LayerNorm(table[ids[r], :] (+ pos_table[pos_ids[r], :])) * gamma + beta,   zeros where row_mask[r] == 0
+ * What Hugging Face's DebertaV2Embeddings.forward computes in front of the encoder the reference replaces
+ * (optimize_deberta keeps `model.embeddings` as it is, deberta.py:322-330) for a model without token types and
+ * without an embedding projection, as an embedding gather, an add, a layer-norm kernel and a multiply; the
+ * reference's benchmark builds its inputs the same way (`table[ids]`, benchmark_cuda.py:176-183).  Same kernel,
+ * limits and fp32 arithmetic as dfl_add_layernorm.  An id outside [0, vocab) (or a position outside
+ * [0, positions)) cannot fault: the row is read as zeros and code 98 is written to `status`, which
+ * dfl_check_status() then reports as DFL_ERR_BAD_ARG.
+ */
+typedef struct DflEmbedLayerNormParams {
+  const void* ids;        /* [rows] int32 or int64 token ids */
+  const void* table;      /* [vocab, hidden] */
+  const void* pos_ids;    /* [rows] or NULL (same integer type as ids) */
+  const void* pos_table;  /* [positions, hidden] or NULL; goes with pos_ids */
+  const void* gamma;      /* [hidden] */
+  const void* beta;       /* [hidden] or NULL */
+  const void* row_mask;   /* [rows] or NULL */
+  void*       out;        /* [rows, hidden] */
+  int64_t rows, vocab, positions;
+  int32_t hidden;
+  float   eps;
+  int32_t dtype;
+  int32_t id_elem_size;   /* 4 or 8 */
+  int32_t mask_elem_size; /* 1, 4 or 8 */
+  int32_t* status;        /* optional device int32, see dfl_check_status() */
+} DflEmbedLayerNormParams;
+DFL_API int dfl_embed_layernorm(const DflEmbedLayerNormParams* p, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
