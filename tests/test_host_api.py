@@ -112,3 +112,47 @@ def test_position_cache_rejects_cpu_and_bad_length():
         cache.compact(0, "cuda")
     with pytest.raises(ValueError, match="CUDA"):
         cache.compact(8, "cpu")
+
+
+def test_fused_embeddings_fall_back_to_the_original_forward_off_the_gpu():
+    """``fuse_deberta_embeddings`` on a CPU model: every call is outside what the kernel covers, so the rebound
+    forward must give the original module's output bit for bit, keep the state-dict keys, and be idempotent."""
+
+    import pytest
+    import torch
+    from torch import nn
+
+    import disentangled_flash_b200 as df
+
+    class Embeddings(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.word_embeddings = nn.Embedding(50, 32, padding_idx=0)
+            self.LayerNorm = nn.LayerNorm(32, 1e-7)
+            self.position_embeddings = None
+            self.position_biased_input = False
+
+        def forward(self, input_ids=None, token_type_ids=None, position_ids=None, mask=None, inputs_embeds=None):
+            hidden = self.LayerNorm(self.word_embeddings(input_ids) if inputs_embeds is None else inputs_embeds)
+            return hidden if mask is None else hidden * mask.unsqueeze(-1).to(hidden.dtype)
+
+    class Model(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.embeddings = Embeddings()
+
+    torch.manual_seed(4)
+    model = Model().eval()
+    keys = sorted(model.state_dict())
+    ids = torch.randint(0, 50, (2, 9))
+    mask = torch.ones(2, 9, dtype=torch.bool)
+    mask[1, 4:] = False
+    want = model.embeddings(input_ids=ids, mask=mask)
+    assert df.fuse_deberta_embeddings(model) is model
+    df.fuse_deberta_embeddings(model)                      # a second call rebinds nothing
+    assert torch.equal(model.embeddings(input_ids=ids, mask=mask), want)
+    assert torch.equal(model.embeddings(ids, None, None, mask), want)
+    model.embeddings.check_device_status()                 # no fused call was made: nothing to report
+    assert sorted(model.state_dict()) == keys
+    with pytest.raises(TypeError):
+        df.fuse_deberta_embeddings(nn.Linear(2, 2))
