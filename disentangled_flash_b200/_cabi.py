@@ -226,7 +226,7 @@ def check_status(status: torch.Tensor) -> None:
     lib = load_library()
     if status.dtype != torch.int32 or status.numel() != 1 or status.device.type != "cuda":
         raise ValueError("status must be a CUDA int32 tensor with one element")
-    with torch.cuda.device(status.device):
+    with _on_device(status.device):
         _check(lib.dfl_check_status(status.data_ptr(), _stream(status.device)), "dfl_check_status")
 
 
@@ -234,7 +234,7 @@ def selftest_bounded_wait(status: torch.Tensor, limit_us: int) -> None:
     """Launch the diagnostic kernel whose only wait can never complete (``dfl_selftest_bounded_wait``)."""
 
     lib = load_library()
-    with torch.cuda.device(status.device):
+    with _on_device(status.device):
         _check(lib.dfl_selftest_bounded_wait(status.data_ptr(), int(limit_us), _stream(status.device)),
                "dfl_selftest_bounded_wait")
 
@@ -246,8 +246,41 @@ def dtype_code(dtype: torch.dtype) -> int:
         raise TypeError("the B200 path supports FP16, BF16, and FP32") from None
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(device: torch.device) -> int:
+    """The current stream of ``device`` as an integer handle (the short way round when torch offers it: a forward
+    of a small batch is bound by what the host spends per launch)."""
+
+    if _raw_stream is not None and device.index is not None:
+        return _raw_stream(device.index)
     return torch.cuda.current_stream(device).cuda_stream
+
+
+class _on_device:
+    """``with _on_device(dev):`` makes ``dev`` the current CUDA device for the call, and costs one query when it
+    already is (``torch.cuda.device`` switches and restores unconditionally)."""
+
+    __slots__ = ("index", "previous")
+
+    def __init__(self, device: torch.device | str):
+        device = torch.device(device)
+        self.index = device.index
+        self.previous = -1
+
+    def __enter__(self) -> None:
+        if self.index is None:
+            return
+        current = torch.cuda.current_device()
+        if current != self.index:
+            self.previous = current
+            torch.cuda.set_device(self.index)
+
+    def __exit__(self, *exc) -> None:
+        if self.previous >= 0:
+            torch.cuda.set_device(self.previous)
+            self.previous = -1
 
 
 def _ptr(t: torch.Tensor | None) -> int | None:
@@ -270,7 +303,7 @@ def build_position_lut(seq_len: int, position_buckets: int, max_relative_positio
         raise ValueError("sequence_length must be positive")
     n = 2 * seq_len - 1
     cap = max(1, min(n, 2 * max(span, 1)))
-    with torch.cuda.device(device):
+    with _on_device(device):
         lut = torch.empty(n, dtype=torch.int32, device=device)
         active = torch.empty(cap, dtype=torch.int64, device=device)
         count = torch.zeros(1, dtype=torch.int32, device=device)
@@ -318,7 +351,7 @@ def linear_heads(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | Non
         p.out[i] = o.data_ptr()
     p.M, p.K, p.n_out, p.heads, p.head_dim, p.rows_per_seq = m, k, n_out, heads, head_dim, rows_per_seq
     p.dtype, p.algo, p.status = dtype_code(x.dtype), algo, _ptr(status)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         _check(lib.dfl_qkv_proj(ctypes.byref(p), _stream(x.device)), "dfl_qkv_proj")
     return outs
 
@@ -331,7 +364,7 @@ def gather_slots(src: torch.Tensor, active: torch.Tensor) -> torch.Tensor:
     heads, n_src, d = src.shape
     n_active = active.numel()
     dst = torch.empty(heads, n_active, d, dtype=src.dtype, device=src.device)
-    with torch.cuda.device(src.device):
+    with _on_device(src.device):
         _check(lib.dfl_gather_slots(src.data_ptr(), active.data_ptr(), dst.data_ptr(), heads, n_src, n_active, d,
                                     dtype_code(src.dtype), _stream(src.device)), "dfl_gather_slots")
     return dst
@@ -356,7 +389,7 @@ def dense(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, *, a
     p.x, p.w, p.bias, p.out = _ptr(x), _ptr(weight), _ptr(bias), _ptr(out)
     p.M, p.N, p.K = x.numel() // k, n, k
     p.activation, p.dtype, p.algo, p.status = activation, dtype_code(x.dtype), algo, _ptr(status)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         _check(lib.dfl_dense(ctypes.byref(p), _stream(x.device)), "dfl_dense")
     return out
 
@@ -406,7 +439,7 @@ def conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, row
         raise ValueError("row_mask must be [B, L]")
     out = torch.empty(x.shape[0], x.shape[1], weight.shape[1], dtype=x.dtype, device=x.device)
     p = _conv1d_params(x, weight, bias, row_mask, out, activation, status)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         _check(lib.dfl_conv1d(ctypes.byref(p), _stream(x.device)), "dfl_conv1d")
     return out
 
@@ -423,7 +456,7 @@ def copy_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor | None = 
     row_bytes = width * src.element_size()
     if out is None:
         out = torch.empty(rows.numel(), width, dtype=src.dtype, device=src.device)
-    with torch.cuda.device(src.device):
+    with _on_device(src.device):
         _check(lib.dfl_copy_rows(src.data_ptr(), out.data_ptr(), rows.data_ptr(), rows.numel(), row_bytes,
                                  _stream(src.device)), "dfl_copy_rows")
     return out
@@ -463,7 +496,7 @@ def embed_layernorm(ids: torch.Tensor, table: torch.Tensor, weight: torch.Tensor
     p.hidden, p.eps, p.dtype, p.id_elem_size = hidden, float(eps), dtype_code(table.dtype), ids.element_size()
     p.mask_elem_size = row_mask.element_size() if row_mask is not None else 1
     p.status = _ptr(status)
-    with torch.cuda.device(table.device):
+    with _on_device(table.device):
         _check(lib.dfl_embed_layernorm(ctypes.byref(p), _stream(table.device)), "dfl_embed_layernorm")
     return out
 
@@ -504,7 +537,7 @@ def add_layernorm(x: torch.Tensor, residual: torch.Tensor | None, weight: torch.
         if out2.dtype != x.dtype or out2.shape[-1] != hidden or out2_rows.dtype != torch.int32 or out2_rows.numel() != p.rows:
             raise ValueError("scatter = (out2 [*, hidden] in the dtype of x, rows int32 [rows of x])")
         p.out2, p.out2_rows = _ptr(out2), _ptr(out2_rows)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         _check(lib.dfl_add_layernorm(ctypes.byref(p), _stream(x.device)), "dfl_add_layernorm")
     return out
 
@@ -532,7 +565,7 @@ def pos_scores(q: torch.Tensor | None, k: torch.Tensor | None, pos_key: torch.Te
     p.batch, p.heads, p.seq_len, p.head_dim = bsz, heads, length, d
     p.n_active, p.ld_slots, p.dtype, p.algo = n_active, ld, dtype_code(ref.dtype), algo
     p.status = _ptr(status)
-    with torch.cuda.device(ref.device):
+    with _on_device(ref.device):
         _check(lib.dfl_pos_scores(ctypes.byref(p), _stream(ref.device)), "dfl_pos_scores")
     return c2p, p2c, ld
 
@@ -555,7 +588,7 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, c2p: torch.
     p.batch, p.heads, p.seq_len, p.head_dim = bsz, heads, length, d
     p.ld_slots, p.mask_elem_size, p.scale = ld_slots, mask.element_size(), scale
     p.dtype, p.algo = dtype_code(q.dtype), algo
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         _check(lib.dfl_attention_fwd(ctypes.byref(p), _stream(q.device)), "dfl_attention_fwd")
     return out
 
@@ -594,7 +627,7 @@ def attention_fwd_static(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_
     for name, t in (("q", q), ("k", k), ("v", v), ("mask", mask), ("out", out)):
         _require_cuda_contiguous(name, t)
     p = _tables_params(q, k, v, pos_key, pos_query, lut, mask, scale, out, algo)
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         _check(lib.dfl_attention_fwd_static(ctypes.byref(p), _stream(q.device)), "dfl_attention_fwd_static")
     return out
 
@@ -609,7 +642,7 @@ def expand_rel_tables(pos: torch.Tensor, lut: torch.Tensor, seq_len: int) -> tor
         raise ValueError("lut must be int32 [2L-1]")
     heads, n_active, d = pos.shape
     rel = torch.empty(heads, 2 * seq_len - 1, d, dtype=pos.dtype, device=pos.device)
-    with torch.cuda.device(pos.device):
+    with _on_device(pos.device):
         _check(lib.dfl_expand_rel_tables(pos.data_ptr(), lut.data_ptr(), rel.data_ptr(), heads, n_active, seq_len, d,
                                          dtype_code(pos.dtype), _stream(pos.device)), "dfl_expand_rel_tables")
     return rel
@@ -664,6 +697,6 @@ def attention_rel_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rel_key
     p.mask, p.out, p.status = mask.data_ptr(), out.data_ptr(), _ptr(status)
     p.batch, p.heads, p.seq_len, p.head_dim = bsz, heads, length, d
     p.mask_elem_size, p.scale, p.dtype, p.algo = mask.element_size(), scale, dtype_code(q.dtype), ALGO_AUTO
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         _check(lib.dfl_attention_rel_fwd(ctypes.byref(p), _stream(q.device)), "dfl_attention_rel_fwd")
     return out

@@ -62,8 +62,8 @@ class B200PreparedPositionPlan(NamedTuple):
 # dfl_qkv_proj, then dfl_attention_rel_fwd where the plan carries relative-distance
 # tables, else dfl_pos_scores + dfl_attention_fwd.
 # --------------------------------------------------------------------------
-@torch.library.custom_op("disentangled_flash_b200::attention_forward", mutates_args=("status",), device_types="cuda")
-def _attention_forward_op(
+def _attention_forward(   # the plain function: what an eager forward calls
+
     hidden_states: torch.Tensor,
     attention_mask: torch.Tensor,
     qkv_weight: torch.Tensor,
@@ -93,6 +93,13 @@ def _attention_forward_op(
         c2p, p2c, ld_slots = _cabi.pos_scores(query, key, pos_key, pos_query, algo=algo, status=status)
     return _cabi.attention_fwd(query, key, value, c2p, p2c, delta_to_local, attention_mask, scale,
                                ld_slots=ld_slots, algo=algo, status=status)
+
+
+# The same function as a custom operator, for a forward that is being traced (``compile_deberta_buckets``): the
+# dispatcher's way into a Python operator costs more host time than some of the kernels run, so an eager forward
+# calls the function directly.
+_attention_forward_op = torch.library.custom_op("disentangled_flash_b200::attention_forward", mutates_args=("status",),
+                                                device_types="cuda")(_attention_forward)
 
 
 @_attention_forward_op.register_fake
@@ -395,7 +402,7 @@ class DisentangledFlashAttention(nn.Module):
         # when relative attention is switched off (_reference.py:277-286).
         scale_factor = 1 + int("c2p" in self.pos_att_type) + int("p2c" in self.pos_att_type)
         uses_lut = self.has_c2p or self.has_p2c
-        output = _attention_forward_op(
+        output = (_attention_forward_op if torch.compiler.is_compiling() else _attention_forward)(
             hidden_states.contiguous(),
             base_mask,
             self._cached_qkv_weight,

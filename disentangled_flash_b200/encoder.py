@@ -61,12 +61,15 @@ class BaseModelOutput:
         return [field for field in fields if field is not None][index]
 
 
-@torch.library.custom_op("disentangled_flash_b200::add_layernorm", mutates_args=(), device_types="cuda")
-def _add_layernorm_op(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
-                      eps: float) -> torch.Tensor:
+def _add_layernorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                   eps: float) -> torch.Tensor:
     """``LayerNorm(x + residual)`` in one pass; sum and statistics in fp32 (``dfl_add_layernorm``)."""
 
     return _cabi.add_layernorm(x.contiguous(), residual.contiguous(), weight, bias, eps)
+
+
+_add_layernorm_op = torch.library.custom_op("disentangled_flash_b200::add_layernorm", mutates_args=(),
+                                            device_types="cuda")(_add_layernorm)
 
 
 @_add_layernorm_op.register_fake
@@ -74,12 +77,15 @@ def _add_layernorm_fake(x, residual, weight, bias, eps):
     return torch.empty_like(x, memory_format=torch.contiguous_format)
 
 
-@torch.library.custom_op("disentangled_flash_b200::dense_gelu", mutates_args=("status",), device_types="cuda")
-def _dense_gelu_op(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
-                   status: Optional[torch.Tensor]) -> torch.Tensor:
+def _dense_gelu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                status: Optional[torch.Tensor]) -> torch.Tensor:
     """``gelu(x @ weight^T + bias)`` (erf form) with bias and activation in the GEMM epilogue (``dfl_dense``)."""
 
     return _cabi.dense(x.contiguous(), weight, bias, activation=_cabi.ACT_GELU, status=status)
+
+
+_dense_gelu_op = torch.library.custom_op("disentangled_flash_b200::dense_gelu", mutates_args=("status",),
+                                         device_types="cuda")(_dense_gelu)
 
 
 @_dense_gelu_op.register_fake
@@ -87,11 +93,10 @@ def _dense_gelu_fake(x, weight, bias, status):
     return x.new_empty(*x.shape[:-1], weight.shape[0])
 
 
-@torch.library.custom_op("disentangled_flash_b200::conv_branch", mutates_args=("status",), device_types="cuda")
-def _conv_branch_op(hidden_states: torch.Tensor, residual: torch.Tensor, attention_mask: torch.Tensor,
-                    conv_weight: torch.Tensor, conv_bias: Optional[torch.Tensor], norm_weight: torch.Tensor,
-                    norm_bias: Optional[torch.Tensor], eps: float, activation: int,
-                    status: Optional[torch.Tensor]) -> torch.Tensor:
+def _conv_branch(hidden_states: torch.Tensor, residual: torch.Tensor, attention_mask: torch.Tensor,
+                 conv_weight: torch.Tensor, conv_bias: Optional[torch.Tensor], norm_weight: torch.Tensor,
+                 norm_bias: Optional[torch.Tensor], eps: float, activation: int,
+                 status: Optional[torch.Tensor]) -> torch.Tensor:
     """The layer-0 convolution branch, ``keep * LayerNorm(residual + act(keep * conv1d(hidden_states)))``
     (``_reference.py:534-568``), as two kernels: ``dfl_conv1d`` (GEMM over the taps with bias, mask and activation in
     its epilogue) and ``dfl_add_layernorm`` (with the mask)."""
@@ -102,6 +107,10 @@ def _conv_branch_op(hidden_states: torch.Tensor, residual: torch.Tensor, attenti
     keep = keep.contiguous()
     out = _cabi.conv1d(hidden_states.contiguous(), conv_weight, conv_bias, keep, activation=activation, status=status)
     return _cabi.add_layernorm(out, residual.contiguous(), norm_weight, norm_bias, eps, out=out, row_mask=keep)
+
+
+_conv_branch_op = torch.library.custom_op("disentangled_flash_b200::conv_branch", mutates_args=("status",),
+                                          device_types="cuda")(_conv_branch)
 
 
 @_conv_branch_op.register_fake
@@ -154,6 +163,13 @@ def _intermediate_is_fusable(block: nn.Module) -> bool:
             and (dense.bias is None or dense.bias.dtype == weight.dtype))
 
 
+def _op(operator, function):
+    """The custom operator while a forward is being traced, the plain function otherwise: the dispatcher's way into
+    a Python operator costs more host time than the smaller kernels run."""
+
+    return operator if torch.compiler.is_compiling() else function
+
+
 _OUTPUT_BLOCK_CHILDREN = frozenset(("dense", "LayerNorm", "dropout"))
 
 
@@ -179,7 +195,7 @@ def _output_block(block: nn.Module, fused: bool, projected: torch.Tensor, residu
     if not fused or projected.dtype != block.LayerNorm.weight.dtype or residual.dtype != projected.dtype:
         return block(projected, residual)
     dense, norm = block.dense, block.LayerNorm
-    return _add_layernorm_op(F.linear(projected, dense.weight, dense.bias), residual, norm.weight, norm.bias,
+    return _op(_add_layernorm_op, _add_layernorm)(F.linear(projected, dense.weight, dense.bias), residual, norm.weight, norm.bias,
                              float(norm.eps))
 
 
@@ -449,7 +465,7 @@ class DebertaV2InferenceEncoder(nn.Module):
             mixed = _output_block(layer.attention.output, fuse_attention_output, context, state)
             if self._fused_intermediates[depth] and mixed.dtype == layer.intermediate.dense.weight.dtype:
                 dense = layer.intermediate.dense
-                inner = _dense_gelu_op(mixed, dense.weight, dense.bias, self._status_word)
+                inner = _op(_dense_gelu_op, _dense_gelu)(mixed, dense.weight, dense.bias, self._status_word)
             else:
                 inner = layer.intermediate(mixed)
             state = _output_block(layer.output, fuse_output, inner, mixed)
@@ -457,7 +473,7 @@ class DebertaV2InferenceEncoder(nn.Module):
                 # the convolution branch sees the encoder input and the padding mask as the caller gave it
                 if self._conv_fused.get(hidden_states.size(1), False) and hidden_states.dtype == state.dtype:
                     norm = self.conv.LayerNorm
-                    state = _conv_branch_op(hidden_states, state, attention_mask, self._conv_weight,
+                    state = _op(_conv_branch_op, _conv_branch)(hidden_states, state, attention_mask, self._conv_weight,
                                             self.conv.conv.bias, norm.weight, norm.bias, float(norm.eps),
                                             self._conv_activation_code, self._status_word)
                 else:
@@ -551,7 +567,7 @@ class DebertaV2InferenceEncoder(nn.Module):
                 # the convolution runs along the sequence: on the unpacked layout, once per forward
                 if self._conv_fused.get(length, False):
                     norm = self.conv.LayerNorm
-                    state_u = _conv_branch_op(hidden_states, state_u, attention_mask, self._conv_weight,
+                    state_u = _conv_branch(hidden_states, state_u, attention_mask, self._conv_weight,
                                               self.conv.conv.bias, norm.weight, norm.bias, float(norm.eps),
                                               self._conv_activation_code, self._status_word)
                 else:
