@@ -699,13 +699,14 @@ class CapturedBucket:
 
 def capture_deberta_buckets(
     encoder: DebertaV2InferenceEncoder,
-    batch_size: int,
+    batch_size: int | Mapping[int, int],
     sequence_lengths: Iterable[int] | None = None,
     *,
     mask_dtype: torch.dtype = torch.bool,
     warmup: int = 2,
 ) -> dict[int, CapturedBucket]:
-    """One CUDA graph per prepared bucket at a fixed batch size.
+    """One CUDA graph per prepared bucket at a fixed batch size (one size for all buckets, or ``{length: size}``,
+    which also selects the buckets).
 
     A forward of a small batch is bound by the rate at which the host can launch kernels (some twenty per layer);
     a captured bucket is launched once.  The reference reaches for ``torch.compile`` here
@@ -714,18 +715,27 @@ def capture_deberta_buckets(
     captured, so that every one-time kernel configuration and lazy module load happens outside the capture.
     """
 
-    if batch_size < 1:
-        raise ValueError("batch_size must be positive")
     table = encoder._buckets
-    lengths = tuple(sorted(table.by_length)) if sequence_lengths is None else table.require(sequence_lengths)
+    if isinstance(batch_size, Mapping):
+        sizes = {int(length): int(size) for length, size in batch_size.items()}
+        lengths = table.require(sorted(sizes) if sequence_lengths is None else sequence_lengths)
+        if any(length not in sizes for length in lengths):
+            raise ValueError("batch_size has no entry for a requested bucket")
+    else:
+        if int(batch_size) < 1:
+            raise ValueError("batch_size must be positive")
+        lengths = tuple(sorted(table.by_length)) if sequence_lengths is None else table.require(sequence_lengths)
+        sizes = {length: int(batch_size) for length in lengths}
+    if any(size < 1 for size in sizes.values()):
+        raise ValueError("batch_size must be positive")
     anchor = encoder._attention_modules()[0].query_proj.weight
     if anchor.device.type != "cuda":
         raise RuntimeError("capture_deberta_buckets needs the encoder on a CUDA device")
     hidden_size = anchor.shape[1]
     captured: dict[int, CapturedBucket] = {}
     # the input buffers are ordinary tensors (callers copy into them outside inference mode)
-    buffers = {length: (torch.zeros(batch_size, length, hidden_size, dtype=anchor.dtype, device=anchor.device),
-                        torch.ones(batch_size, length, dtype=mask_dtype, device=anchor.device)) for length in lengths}
+    buffers = {length: (torch.zeros(sizes[length], length, hidden_size, dtype=anchor.dtype, device=anchor.device),
+                        torch.ones(sizes[length], length, dtype=mask_dtype, device=anchor.device)) for length in lengths}
     with torch.cuda.device(anchor.device), torch.inference_mode():
         for length in lengths:
             plans = table.by_length[length]
