@@ -147,6 +147,17 @@ def test_captured_buckets_replay_the_eager_forward_bitwise():
     encoder.check_device_status()
     with pytest.raises(ValueError, match="captured for"):
         graphs[64](torch.zeros(2, 64, 128, dtype=torch.float16, device=dev), torch.ones(2, 64, dtype=torch.bool, device=dev))
+    # a batch size per bucket (which also selects the buckets)
+    sized = df.capture_deberta_buckets(encoder, {160: 2})
+    assert sorted(sized) == [160] and sized[160].hidden_states.shape == (2, 160, 128)
+    hidden = torch.randn(2, 160, 128, generator=gen).mul_(0.5).to(torch.float16).to(dev)
+    mask = torch.ones(2, 160, dtype=torch.bool, device=dev)
+    encoder.activate_shape(160)
+    with torch.inference_mode():
+        want = encoder(hidden, mask, output_hidden_states=False).last_hidden_state
+    assert torch.equal(sized[160](hidden, mask), want)
+    with pytest.raises(ValueError):
+        df.capture_deberta_buckets(encoder, {160: 2}, sequence_lengths=[64])
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
